@@ -1,0 +1,127 @@
+/* libspio_b200 -- C ABI of the B200 (sm_100a) group-width-8 convolution path.
+ *
+ * Every entry point takes plain pointers and sizes.  Device-pointer entry points
+ * enqueue work on the given CUDA stream (a cudaStream_t passed as void*, NULL = the
+ * legacy default stream) and return without synchronising.  All return 0 on success
+ * and a non-zero code on failure; spio_b200_last_error() gives the message of the last
+ * failure on the calling thread.
+ *
+ * Tensor layouts (the ones the reference's kernels take):
+ *   activations and gradients  NHWC fp16            (torch channels_last of (N,C,H,W))
+ *   weight                     [K][R][S][8] fp16    (torch channels_last of (K,8,R,S)), K == C
+ *   bias                       [K] fp32 or NULL
+ *   weight gradient            [K][R][S][8] fp32
+ * Stride 1, dilation 1, 1 <= R,S <= 5, C a multiple of 8, P = H + 2*pad_h - R + 1,
+ * Q = W + 2*pad_w - S + 1.  Device pointers must be 16-byte aligned.
+ */
+#ifndef SPIO_B200_H_
+#define SPIO_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Problem shape; mirrors spio.kernels.Conv2dGw8Params
+ * (reference: spio/kernels/conv2d_gw8_params.py:10-44). */
+typedef struct spio_gw8_shape {
+  int n, c, h, w;     /* input batch, channels, height, width */
+  int r, s;           /* filter height, width */
+  int pad_h, pad_w;   /* zero padding */
+} spio_gw8_shape;
+
+/* Tile configuration; every zero field is chosen by the library.  Plays the role of
+ * the reference's Conv2dGw8Config / Conv2dGw8WgradConfig
+ * (spio/kernels/conv2d_gw8_kernel.py:30-36, conv2d_gw8_wgrad_kernel.py:27-35). */
+typedef struct spio_gw8_tune {
+  int wpg;   /* compute warps per channel group: 1, 2 or 3 */
+  int tpw;   /* 8-pixel x 2-row tiles per warp */
+  int ns;    /* shared-memory ring slots */
+  int nob;   /* output staging buffers (fprop / dgrad) */
+  int ncb;   /* 8-pixel column blocks per column tile */
+  int nb;    /* images per ring slot */
+  int grid;  /* CTAs; 0 = one per SM */
+} spio_gw8_tune;
+
+/* What a launch will look like; filled by spio_conv2d_gw8_plan. */
+typedef struct spio_gw8_plan_info {
+  int wpg, tpw, ns, nob, ncb, nb, grid, threads;
+  int smem_bytes;
+  int n_chunks, n_image_groups, n_col_tiles, n_pairs, n_split;
+  size_t scratch_bytes; /* wgrad only */
+} spio_gw8_plan_info;
+
+enum {
+  SPIO_GW8_FPROP = 0,
+  SPIO_GW8_DGRAD = 1,
+  SPIO_GW8_WGRAD = 2
+};
+
+/* Forward: y = conv2d(x, w, groups = C/8) + bias.
+ * Replaces the launch of the reference kernel spio_conv2d_gw8_fprop__<params>
+ * (spio/src/conv2d_gw8.cu:10-12; launched by spio/kernels/kernel.py:135-154 from
+ * spio/functional/conv2d_gw8_function.py:59-62). */
+int spio_conv2d_gw8_fprop(void* y, const void* x, const void* w, const float* bias,
+                          const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* stream);
+
+/* Input gradient: dx = conv2d_transpose(dy, w).  dy is (N,P,Q,K), dx is (N,H,W,C).
+ * Replaces spio_conv2d_gw8_dgrad__<params> (spio/src/conv2d_gw8.cu:10-12 with
+ * Mode::igrad, :99-105; called at spio/functional/conv2d_gw8_function.py:140-144). */
+int spio_conv2d_gw8_dgrad(void* dx, const void* dy, const void* w,
+                          const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* stream);
+
+/* Bytes of device scratch spio_conv2d_gw8_wgrad needs for this shape and tuning. */
+size_t spio_conv2d_gw8_wgrad_scratch_bytes(const spio_gw8_shape* shape,
+                                           const spio_gw8_tune* tune);
+
+/* Weight gradient: dw = sum over pixels of x (shifted) * dy, fp32.  dw is overwritten
+ * (it need not be zeroed first) and the summation order is fixed.  `scratch` is device
+ * memory of at least spio_conv2d_gw8_wgrad_scratch_bytes(); its contents on entry do
+ * not matter.  Replaces spio_conv2d_gw8_wgrad__<params>
+ * (spio/src/conv2d_gw8_wgrad.cu:10-12) together with the zero fill that precedes it
+ * (spio/functional/conv2d_gw8_function.py:125-130). */
+int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy,
+                          const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                          void* scratch, size_t scratch_bytes, void* stream);
+
+/* Host-buffer variants: copy the operands to the device, run, copy the result back and
+ * wait for it.  Device staging buffers are owned by the library and grow on demand.
+ * Pinned host memory makes the copies asynchronous; pageable memory also works. */
+int spio_conv2d_gw8_fprop_host(void* y, const void* x, const void* w, const float* bias,
+                               const spio_gw8_shape* shape, const spio_gw8_tune* tune);
+int spio_conv2d_gw8_dgrad_host(void* dx, const void* dy, const void* w,
+                               const spio_gw8_shape* shape, const spio_gw8_tune* tune);
+int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy,
+                               const spio_gw8_shape* shape, const spio_gw8_tune* tune);
+
+/* Reports the launch the library would make; kind is SPIO_GW8_FPROP/DGRAD/WGRAD.
+ * Needs a CUDA device (it reads the SM count and the shared-memory limit). */
+int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                         spio_gw8_plan_info* info);
+
+/* The same plan for a device with the given SM count and opt-in shared-memory limit;
+ * touches no device, so it also works on a machine without a GPU. */
+int spio_conv2d_gw8_plan_for(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                             int sm_count, int smem_optin_bytes, spio_gw8_plan_info* info);
+
+/* Number of compiled (r, s, wpg, tpw) variants, and the i-th one. */
+int spio_conv2d_gw8_num_variants(void);
+int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw);
+
+/* Kernels record a bounded wait that gave up in a per-device status word.  This call
+ * synchronises the current device, returns the word through *status (0 = ok) and clears
+ * it.  Corresponds to the reference's error path in spio/cuda/driver.pyx:118-123. */
+int spio_b200_device_status(int* status);
+
+/* Message of the last failure on this thread ("" if none). */
+const char* spio_b200_last_error(void);
+
+/* Library version string. */
+const char* spio_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SPIO_B200_H_ */

@@ -1,0 +1,128 @@
+"""ctypes binding of libspio_b200.so, the C-ABI library declared in include/spio_b200.h.
+
+Takes the place of the reference's Cython driver module (spio/cuda/driver.pyx) as the
+one native boundary of the package.  There is no CPU fallback: if the library is missing
+or fails to load, every operator raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_size_t, c_void_p
+from pathlib import Path
+from typing import Optional
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libspio_b200.so"
+
+FPROP, DGRAD, WGRAD = 0, 1, 2
+
+
+class Shape(Structure):
+    """struct spio_gw8_shape."""
+
+    _fields_ = [(k, c_int) for k in ("n", "c", "h", "w", "r", "s", "pad_h", "pad_w")]
+
+
+class Tune(Structure):
+    """struct spio_gw8_tune; zero fields are chosen by the library."""
+
+    _fields_ = [(k, c_int) for k in ("wpg", "tpw", "ns", "nob", "ncb", "nb", "grid")]
+
+
+class PlanInfo(Structure):
+    """struct spio_gw8_plan_info."""
+
+    _fields_ = [
+        (k, c_int)
+        for k in (
+            "wpg", "tpw", "ns", "nob", "ncb", "nb", "grid", "threads", "smem_bytes",
+            "n_chunks", "n_image_groups", "n_col_tiles", "n_pairs", "n_split",
+        )
+    ] + [("scratch_bytes", c_size_t)]
+
+    def as_dict(self):
+        return {name: getattr(self, name) for name, _ in self._fields_}
+
+
+# name -> (restype, argtypes); one entry per symbol declared in include/spio_b200.h
+SIGNATURES = {
+    "spio_conv2d_gw8_fprop": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
+    "spio_conv2d_gw8_dgrad": (
+        c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
+    "spio_conv2d_gw8_wgrad_scratch_bytes": (c_size_t, [POINTER(Shape), POINTER(Tune)]),
+    "spio_conv2d_gw8_wgrad": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p, c_size_t, c_void_p]),
+    "spio_conv2d_gw8_fprop_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune)]),
+    "spio_conv2d_gw8_dgrad_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune)]),
+    "spio_conv2d_gw8_wgrad_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune)]),
+    "spio_conv2d_gw8_plan": (c_int, [c_int, POINTER(Shape), POINTER(Tune), POINTER(PlanInfo)]),
+    "spio_conv2d_gw8_plan_for": (
+        c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),
+    "spio_conv2d_gw8_num_variants": (c_int, []),
+    "spio_conv2d_gw8_variant": (
+        c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
+    "spio_b200_device_status": (c_int, [POINTER(c_int)]),
+    "spio_b200_last_error": (c_char_p, []),
+    "spio_b200_version": (c_char_p, []),
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once and attach the argument types."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m spio_b200.build` "
+            "(there is no fallback implementation)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().spio_b200_last_error().decode()
+
+
+def check(rc: int, what: str = "") -> None:
+    """Raise ValueError (the reference's convention for CUDA errors,
+    spio/cuda/driver.pyx:118-123) when a call returned non-zero."""
+    if rc != 0:
+        msg = last_error()
+        raise ValueError(f"{msg}" + (f" [{what}]" if what else ""))
+
+
+def make_tune(tune) -> Optional[Tune]:
+    """Accept None, a Tune, or a mapping / object with the tune's field names."""
+    if tune is None:
+        return None
+    if isinstance(tune, Tune):
+        return tune
+    if isinstance(tune, dict):
+        return Tune(**{k: int(v) for k, v in tune.items()})
+    return Tune(**{k: int(getattr(tune, k, 0)) for k, _ in Tune._fields_})
+
+
+def tune_ref(tune):
+    t = make_tune(tune)
+    return ctypes.byref(t) if t is not None else None
+
+
+def device_status() -> int:
+    """Synchronise the current device and return (and clear) its kernel status word."""
+    st = c_int(0)
+    check(load().spio_b200_device_status(ctypes.byref(st)), "device_status")
+    return st.value

@@ -1,0 +1,287 @@
+// Group-width-8 convolution, weight gradient, for sm_100a.
+//
+//   dw[k,r,s,c] = sum_{n,p,q} x[n,p+r-pad_h,q+s-pad_w,c] * dy[n,p,q,k]     (c in group(k))
+//
+// x and dy are NHWC fp16, dw is [K][R][S][8] fp32.  Same arithmetic contract as the
+// reference kernel spio/src/conv2d_gw8_wgrad.cu:10-226, which sums CTA partials with
+// fp32 atomicAdd into a pre-zeroed buffer (:207-224).  Here the sum is two-level and
+// has a fixed order: every compute warp keeps its taps x 8 x 8 partial in registers for
+// its whole share of the pixels and writes it once to a scratch buffer; a second small
+// kernel adds the partials of a chunk in a fixed order and overwrites dw, so dw needs no
+// zero fill and the result does not vary from run to run.
+//
+// Mapping: per group the contraction is M = two taps x 8 in-channels, N = 8 out-channels,
+// K = 16 pixels (8 columns of two output rows), mma.sync m16n8k16; both operands come
+// from shared memory with ldmatrix.trans.  x rows are read once and kept in a register
+// window exactly as in the forward kernel; pixels outside the image contribute nothing
+// because the tiled copy of dy zero-fills them.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "conv2d_gw8_fwd.cuh"
+
+namespace spio_b200 {
+
+// Scratch layout: [chunk][part][64 local out-channels][taps][8 in-channels] fp32 with
+// part = split * WPG + warp_sub, n_parts = n_split * WPG.
+template <class Cfg>
+__global__ void __launch_bounds__((Cfg::NCW + 1) * 32, 1)
+conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
+                        const __grid_constant__ TensorMap dy_map, const Gw8Geom g,
+                        float* __restrict__ scratch, int ns, int* __restrict__ status) {
+  constexpr int S = Cfg::S, WPG = Cfg::WPG, TPW = Cfg::TPW;
+  constexpr int E = Cfg::E, WIN = Cfg::WIN, NT = Cfg::NT, NCW = Cfg::NCW;
+  constexpr int NPH = WIN / 2;
+  constexpr int NACC = (NT + 1) / 2;
+  constexpr int MAX_NS = 16;
+
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) u64 bars[2 * MAX_NS];
+  __shared__ int abort_flag;
+
+  const u32 base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const u32 xslot_bytes = (u32)(g.nb * 2 * g.bw) * 128u;
+  const u32 dslot_bytes = (u32)(g.nb * 2 * g.wt) * 128u;
+  const u32 stage_bytes = xslot_bytes + dslot_bytes;
+  const u32 bar0 = smem_u32(bars);
+  auto full = [&](int i) { return bar0 + 8u * (u32)i; };
+  auto empty = [&](int i) { return bar0 + 8u * (u32)(MAX_NS + i); };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ns; ++i) {
+      mbar_init(full(i), 1);
+      mbar_init(empty(i), NCW);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // CTA b works on split `si` of chunks cl, cl + chunk_step, ...
+  const int si = blockIdx.x % g.n_split;
+  const int cl = blockIdx.x / g.n_split;
+  const int chunk_step = gridDim.x / g.n_split;
+  const int per_chunk = g.n_ig * g.n_ct * g.n_pairs;
+  const int s0 = gw8_span_begin(per_chunk, si, g.n_split);
+  const int s1 = gw8_span_begin(per_chunk, si + 1, g.n_split);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == NCW) {
+    // ------------------------------------------------------------ load warp
+    if (lane == 0) {
+      prefetch_tensormap(&x_map);
+      prefetch_tensormap(&dy_map);
+      int slot = 0;
+      u32 par = 0;
+      bool ok = true;
+      for (int ck = cl; ok && ck < g.n_chunks; ck += chunk_step) {
+        Gw8Walk walk(ck * per_chunk + s0, ck * per_chunk + s1, g);
+        Gw8Segment seg;
+        while (ok && walk.next(seg)) {
+          const int nst = seg.m1 - seg.m0 + E;
+          const int c0 = seg.ck * 64;
+          const int n0 = seg.ig * g.nb;
+          for (int j = 0; j < nst; ++j) {
+            if (!mbar_wait(empty(slot), par ^ 1u, abortp)) {
+              ok = false;
+              break;
+            }
+            const u32 dst = base + (u32)slot * stage_bytes;
+            mbar_arrive_expect_tx(full(slot), j >= E ? stage_bytes : xslot_bytes);
+            tma_load_4d(dst, &x_map, full(slot), c0, seg.ct * g.wt - g.pad_w,
+                        2 * (seg.m0 + j) - g.pad_h, n0);
+            if (j >= E)
+              tma_load_4d(dst + xslot_bytes, &dy_map, full(slot), c0, seg.ct * g.wt,
+                          2 * (seg.m0 + j - E), n0);
+            if (++slot == ns) {
+              slot = 0;
+              par ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ compute warps
+    const int grp = warp & 7;
+    const int wsub = warp >> 3;
+    const u32 l7 = lane & 7;
+    const int gq = lane >> 2;
+    const int t4 = lane & 3;
+
+    constexpr int NMAT = 2 * S;
+    constexpr int NLD4 = NMAT / 4;
+    constexpr bool LD2 = (NMAT % 4) != 0;
+    constexpr int NLD = NLD4 + (LD2 ? 1 : 0);
+    u32 ld_off[NLD];
+#pragma unroll
+    for (int q = 0; q < NLD; ++q) {
+      int f = 4 * q + (lane >> 3);
+      if (LD2 && q == NLD4) f = 4 * q + ((lane >> 3) & 1);
+      const u32 rowsel = (u32)(f / S), s = (u32)(f % S);
+      ld_off[q] = (rowsel * (u32)g.bw + s + l7) * 128u + (((u32)grp ^ ((s + l7) & 7u)) << 4);
+    }
+    // dy: matrix 0 = the 8 pixels of the top row, matrix 1 = bottom row
+    const u32 dy_off = ((u32)((lane >> 3) & 1) * (u32)g.wt + l7) * 128u + (((u32)grp ^ l7) << 4);
+
+    u32 x_off[TPW], d_off[TPW];
+    bool tile_on[TPW];
+#pragma unroll
+    for (int t = 0; t < TPW; ++t) {
+      const int tidx = wsub + WPG * t;
+      tile_on[t] = tidx < g.ntiles;
+      const int img = tidx / g.ncb, cb = tidx % g.ncb;
+      x_off[t] = (u32)(img * 2 * g.bw + cb * 8) * 128u;
+      d_off[t] = (u32)(img * 2 * g.wt + cb * 8) * 128u;
+    }
+
+    u32 X[TPW][WIN][S];
+    float acc[NACC][4];
+    int slot = 0;
+    u32 par = 0;
+    bool ok = true;
+    const int n_parts = g.n_split * WPG;
+
+    for (int ck = cl; ok && ck < g.n_chunks; ck += chunk_step) {
+      const bool grp_on = (ck * 64 + grp * 8) < g.c;
+#pragma unroll
+      for (int i = 0; i < NACC; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+
+      Gw8Walk walk(ck * per_chunk + s0, ck * per_chunk + s1, g);
+      Gw8Segment seg;
+      while (ok && walk.next(seg)) {
+        const int nst = seg.m1 - seg.m0 + E;
+
+        auto stage = [&](auto phc, int j) -> bool {
+          constexpr int PH = decltype(phc)::value;
+          if (!mbar_wait(full(slot), par, abortp)) return false;
+          const u32 xbase = base + (u32)slot * stage_bytes;
+          const u32 dbase = xbase + xslot_bytes;
+          if (grp_on) {
+#pragma unroll
+            for (int t = 0; t < TPW; ++t) {
+              if (tile_on[t]) {
+                const u32 a = xbase + x_off[t];
+#pragma unroll
+                for (int q = 0; q < NLD4; ++q) {
+                  const int f0 = 4 * q;
+                  ldmatrix_x4<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
+                                    X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
+                                    X[t][2 * PH + (f0 + 2) / S][(f0 + 2) % S],
+                                    X[t][2 * PH + (f0 + 3) / S][(f0 + 3) % S], a + ld_off[q]);
+                }
+                if (LD2) {
+                  const int f0 = 4 * NLD4;
+                  ldmatrix_x2<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
+                                    X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
+                                    a + ld_off[NLD - 1]);
+                }
+                if (j >= E) {
+                  u32 d0, d1;
+                  ldmatrix_x2<true>(d0, d1, dbase + d_off[t] + dy_off);
+#pragma unroll
+                  for (int i = 0; i < NACC; ++i) {
+                    const int fa = 2 * i, fb = 2 * i + 1;
+                    const int ra = fa / S, sa = fa % S;
+                    const int pa0 = 2 * ((PH + 1 + ra / 2) % NPH) + (ra & 1);
+                    const int pa1 = 2 * ((PH + 1 + (ra + 1) / 2) % NPH) + ((ra + 1) & 1);
+                    if (fb < NT) {
+                      const int rb = fb / S, sb = fb % S;
+                      const int pb0 = 2 * ((PH + 1 + rb / 2) % NPH) + (rb & 1);
+                      const int pb1 = 2 * ((PH + 1 + (rb + 1) / 2) % NPH) + ((rb + 1) & 1);
+                      mma_m16n8k16(acc[i], X[t][pa0][sa], X[t][pb0][sb], X[t][pa1][sa],
+                                   X[t][pb1][sb], d0, d1);
+                    } else {
+                      mma_m16n8k16(acc[i], X[t][pa0][sa], 0u, X[t][pa1][sa], 0u, d0, d1);
+                    }
+                  }
+                }
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty(slot));
+          if (++slot == ns) {
+            slot = 0;
+            par ^= 1u;
+          }
+          return true;
+        };
+
+        for (int j = 0; ok && j < nst; j += NPH) {
+          ok = stage(IntC<0>{}, j);
+          if (NPH > 1 && ok && j + 1 < nst) ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, j + 1);
+          if (NPH > 2 && ok && j + 2 < nst) ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, j + 2);
+        }
+      }
+
+      // Flush this warp's partial: acc[i] = {(tap 2i, c=g, k=2t), (.., k=2t+1),
+      //                                      (tap 2i+1, c=g, k=2t), (.., k=2t+1)}.
+      float* part = scratch + ((size_t)ck * n_parts + (size_t)(si * WPG + wsub)) * (64 * NT * 8);
+      const int kl = grp * 8 + 2 * t4;
+#pragma unroll
+      for (int i = 0; i < NACC; ++i) {
+        const int fa = 2 * i, fb = 2 * i + 1;
+        part[((kl + 0) * NT + fa) * 8 + gq] = acc[i][0];
+        part[((kl + 1) * NT + fa) * 8 + gq] = acc[i][1];
+        if (fb < NT) {
+          part[((kl + 0) * NT + fb) * 8 + gq] = acc[i][2];
+          part[((kl + 1) * NT + fb) * 8 + gq] = acc[i][3];
+        }
+      }
+    }
+  }
+
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    if (threadIdx.x == 0) atomicExch(status, (int)GW8_WAIT_TIMEOUT);
+  }
+}
+
+// dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], parts added
+// in index order.  blockDim = (32, RW): lanes run over float4 columns, warps over parts.
+template <int RW>
+__global__ void __launch_bounds__(32 * RW)
+conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__ scratch, int c,
+                               int taps, int n_parts) {
+  __shared__ float4 red[RW][32];
+  const int chunk_f4 = 64 * taps * 8 / 4;        // float4 per chunk
+  const int total_f4 = c * taps * 8 / 4;         // float4 in dw
+  const int col = blockIdx.x * 32 + threadIdx.x;  // float4 index into dw
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (col < total_f4) {
+    const int ck = col / chunk_f4;
+    const int e = col - ck * chunk_f4;
+    const float4* src =
+        reinterpret_cast<const float4*>(scratch) + (size_t)ck * n_parts * chunk_f4 + e;
+#pragma unroll 4
+    for (int p = threadIdx.y; p < n_parts; p += RW) {
+      const float4 v = src[(size_t)p * chunk_f4];
+      sum.x += v.x;
+      sum.y += v.y;
+      sum.z += v.z;
+      sum.w += v.w;
+    }
+  }
+  red[threadIdx.y][threadIdx.x] = sum;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < total_f4) {
+#pragma unroll
+    for (int w = 1; w < RW; ++w) {
+      const float4 v = red[w][threadIdx.x];
+      sum.x += v.x;
+      sum.y += v.y;
+      sum.z += v.z;
+      sum.w += v.w;
+    }
+    reinterpret_cast<float4*>(dw)[col] = sum;
+  }
+}
+
+}  // namespace spio_b200

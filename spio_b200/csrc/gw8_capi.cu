@@ -1,0 +1,546 @@
+// C ABI of libspio_b200 (declared in include/spio_b200.h): planning and launch of the
+// gw8 forward / input-gradient / weight-gradient kernels.
+//
+// Host-side counterpart of the reference's launch path
+//   spio/kernels/kernel.py:135-154 (Kernel.launch) -> spio/cuda/driver.pyx:171-208
+// with the per-shape kernel specification (spio/kernels/conv2d_gw8_kernel.py:62-238,
+// conv2d_gw8_wgrad_kernel.py:92-285) replaced by a launch-time plan.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/spio_b200.h"
+#include "conv2d_gw8_wgrad.cuh"
+#include "gw8_host.h"
+
+namespace spio_b200 {
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(const std::string& msg) {
+  g_last_error = msg;
+  return 1;
+}
+
+int fail_cuda(const char* what, cudaError_t e) {
+  return fail(std::string("CUDA error: ") + cudaGetErrorString(e) + " (" + what + ")");
+}
+
+#define GW8_CUDA(call)                                   \
+  do {                                                   \
+    cudaError_t e_ = (call);                             \
+    if (e_ != cudaSuccess) return fail_cuda(#call, e_);  \
+  } while (0)
+
+// Status word the kernels write when a bounded wait gives up; one per device because
+// the symbol is instantiated in every context that loads the library.
+__device__ int g_status_word;
+
+constexpr int kMaxDevices = 64;
+constexpr int kFwdStaticSmem = 512;    // >= static shared memory of the kernels
+constexpr int kAlignSlack = 1024;      // dynamic shared memory is re-aligned to 1 KiB
+
+struct DeviceInfo {
+  bool ready = false;
+  int sms = 0;
+  int smem_optin = 0;
+  int* status = nullptr;
+};
+
+std::mutex g_mutex;
+DeviceInfo g_devices[kMaxDevices];
+std::vector<Gw8Variant> g_variants;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+void load_variants_locked() {
+  if (!g_variants.empty()) return;
+  const Gw8Variant* v = nullptr;
+  int n;
+  n = gw8_variants_r1(&v);
+  g_variants.insert(g_variants.end(), v, v + n);
+  n = gw8_variants_r2(&v);
+  g_variants.insert(g_variants.end(), v, v + n);
+  n = gw8_variants_r3(&v);
+  g_variants.insert(g_variants.end(), v, v + n);
+  n = gw8_variants_r4(&v);
+  g_variants.insert(g_variants.end(), v, v + n);
+  n = gw8_variants_r5(&v);
+  g_variants.insert(g_variants.end(), v, v + n);
+}
+
+// Per-device set-up: limits, the status word's device address, the driver entry point
+// for tensor-map encoding and the opt-in shared-memory size of every kernel.
+int device_info(const DeviceInfo** out) {
+  int dev = 0;
+  GW8_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_mutex);
+  load_variants_locked();
+  DeviceInfo& d = g_devices[dev];
+  if (!d.ready) {
+    GW8_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+    GW8_CUDA(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    int major = 0;
+    GW8_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10)
+      return fail("unsupported device: libspio_b200 is built for sm_100a only");
+    GW8_CUDA(cudaGetSymbolAddress((void**)&d.status, g_status_word));
+    GW8_CUDA(cudaMemset(d.status, 0, sizeof(int)));
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      GW8_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+        return fail("cuTensorMapEncodeTiled is not available from this driver");
+      g_encode = (EncodeTiledFn)fn;
+    }
+    for (const Gw8Variant& v : g_variants) {
+      GW8_CUDA(cudaFuncSetAttribute(v.fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    d.smem_optin - kFwdStaticSmem));
+      GW8_CUDA(cudaFuncSetAttribute(v.wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    d.smem_optin - kFwdStaticSmem));
+    }
+    d.ready = true;
+  }
+  *out = &d;
+  return 0;
+}
+
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+inline int round_up(int a, int b) { return cdiv(a, b) * b; }
+
+struct Plan {
+  int kind = 0;
+  const Gw8Variant* v = nullptr;
+  Gw8Geom g{};
+  int ns = 0, nob = 0, grid = 0, threads = 0;
+  int smem = 0;
+  size_t scratch_bytes = 0;
+};
+
+int check_shape(const spio_gw8_shape* sh) {
+  if (sh == nullptr) return fail("shape is NULL");
+  if (sh->n <= 0 || sh->c <= 0 || sh->h <= 0 || sh->w <= 0) return fail("n, c, h, w must be positive");
+  if (sh->c % 8 != 0) return fail("Number of channels must be divisible by group width.");
+  if (sh->r < 1 || sh->r > 5) return fail("Kernel height must be between 1 and 5.");
+  if (sh->s < 1 || sh->s > 5) return fail("Kernel width must be between 1 and 5.");
+  if (sh->pad_h < 0 || sh->pad_w < 0) return fail("padding must be non-negative");
+  const int p = sh->h + 2 * sh->pad_h - sh->r + 1;
+  const int q = sh->w + 2 * sh->pad_w - sh->s + 1;
+  if (p <= 0 || q <= 0) return fail("output height / width must be positive");
+  return 0;
+}
+
+// The plan needs only the SM count and the shared-memory limit, so it can be computed
+// (and unit-tested) without a device.
+int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
+              const std::vector<Gw8Variant>& variants, Plan* plan) {
+  if (check_shape(sh)) return 1;
+  static const spio_gw8_tune kAuto = {0, 0, 0, 0, 0, 0, 0};
+  const spio_gw8_tune& t = tune ? *tune : kAuto;
+  const int p = sh->h + 2 * sh->pad_h - sh->r + 1;
+  const int q = sh->w + 2 * sh->pad_w - sh->s + 1;
+
+  const Gw8Variant* v = nullptr;
+  for (const Gw8Variant& cand : variants) {
+    if (cand.r != sh->r || cand.s != sh->s) continue;
+    if (t.wpg && cand.wpg != t.wpg) continue;
+    if (t.tpw && cand.tpw != t.tpw) continue;
+    v = &cand;
+    break;
+  }
+  if (v == nullptr) return fail("no compiled kernel variant matches r, s, wpg, tpw");
+
+  Plan pl;
+  pl.kind = kind;
+  pl.v = v;
+  Gw8Geom& g = pl.g;
+  g.n = sh->n;
+  g.c = sh->c;
+  g.dgrad = kind == SPIO_GW8_DGRAD;
+  if (kind == SPIO_GW8_DGRAD) {
+    g.in_h = p, g.in_w = q, g.out_h = sh->h, g.out_w = sh->w;
+    g.pad_h = sh->r - 1 - sh->pad_h, g.pad_w = sh->s - 1 - sh->pad_w;
+  } else {
+    g.in_h = sh->h, g.in_w = sh->w, g.out_h = p, g.out_w = q;
+    g.pad_h = sh->pad_h, g.pad_w = sh->pad_w;
+  }
+  const int max_tiles = v->wpg * v->tpw;
+  const int e = sh->r / 2;
+  const int avail = smem_optin - kFwdStaticSmem - kAlignSlack;
+  const int qb = cdiv(g.out_w, 8);
+
+  int ncb = t.ncb ? t.ncb : 0;
+  if (ncb <= 0) {
+    const int n_ct0 = cdiv(qb, max_tiles);
+    ncb = cdiv(qb, n_ct0);
+  }
+  if (ncb > max_tiles) return fail("ncb exceeds wpg * tpw");
+  int nb = t.nb ? t.nb : 0;
+  if (nb <= 0) {
+    nb = 1;
+    if (ncb >= qb) {  // the whole width fits one column tile: batch images into a slot
+      nb = max_tiles / ncb;
+      if (nb > sh->n) nb = sh->n;
+      if (nb < 1) nb = 1;
+    }
+  }
+  if (nb * ncb > max_tiles) return fail("nb * ncb exceeds wpg * tpw");
+
+  const int min_slots = e + 2;
+  for (;;) {
+    g.ncb = ncb;
+    g.nb = nb;
+    g.wt = 8 * ncb;
+    g.bw = round_up(g.wt + sh->s - 1, 8);
+    const int slot = nb * 2 * g.bw * 128;
+    const int oslot = nb * 2 * g.wt * 128;
+    int ns, nob = 0;
+    if (kind == SPIO_GW8_WGRAD) {
+      ns = avail / (slot + oslot);
+    } else {
+      nob = t.nob ? t.nob : 2;
+      if (nob > 4) return fail("nob must be at most 4");
+      ns = (avail - nob * oslot) / slot;
+    }
+    if (ns > 16) ns = 16;
+    if (t.ns) {
+      if (t.ns > ns) return fail("requested ring does not fit in shared memory");
+      ns = t.ns;
+    }
+    const bool box_ok = g.bw <= 256 && nb <= 256;
+    if (ns >= min_slots && box_ok && (t.nb || t.ncb || slot <= 32 * 1024 || (nb == 1 && ncb == 1))) {
+      pl.ns = ns;
+      pl.nob = nob;
+      pl.smem = kAlignSlack + ns * (kind == SPIO_GW8_WGRAD ? slot + oslot : slot) + nob * oslot;
+      break;
+    }
+    if (t.nb || t.ncb) return fail("requested tile does not fit in shared memory");
+    if (nb > 1)
+      nb = nb / 2;
+    else if (ncb > 1)
+      ncb = cdiv(ncb, 2);
+    else
+      return fail("tile does not fit in shared memory");
+  }
+  g.ntiles = g.nb * g.ncb;
+  g.n_chunks = cdiv(g.c, 64);
+  g.n_ig = cdiv(g.n, g.nb);
+  g.n_ct = cdiv(qb, g.ncb);
+  g.n_pairs = cdiv(g.out_h, 2);
+  const long long per_chunk = (long long)g.n_ig * g.n_ct * g.n_pairs;
+  const long long total = per_chunk * g.n_chunks;
+  if (total > 0x7fffffffLL / 2) return fail("problem too large for 32-bit work indices");
+  const int ctas = t.grid > 0 ? t.grid : sms;
+  g.n_split = 1;
+  if (kind == SPIO_GW8_WGRAD) {
+    pl.threads = v->wgrad_threads;
+    if (g.n_chunks <= ctas) {
+      long long split = ctas / g.n_chunks;
+      if (split > per_chunk) split = per_chunk;
+      g.n_split = (int)split;
+      pl.grid = g.n_split * g.n_chunks;
+    } else {
+      pl.grid = ctas;
+    }
+    pl.scratch_bytes = (size_t)g.n_chunks * g.n_split * v->wpg * 64 * sh->r * sh->s * 8 * sizeof(float);
+  } else {
+    pl.threads = v->fwd_threads;
+    pl.grid = (int)(total < ctas ? total : ctas);
+  }
+  *plan = pl;
+  return 0;
+}
+
+int encode_map(CUtensorMap* m, const void* ptr, int c, int w, int h, int n, int box_w, int box_n) {
+  if ((reinterpret_cast<size_t>(ptr) & 15u) != 0) return fail("tensor pointers must be 16-byte aligned");
+  const cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
+  const cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};
+  const cuuint32_t box[4] = {64u, (cuuint32_t)box_w, 2u, (cuuint32_t)box_n};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(ptr), dims,
+                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    snprintf(buf, sizeof buf,
+             "CUDA error: cuTensorMapEncodeTiled failed with code %d (dims %d,%d,%d,%d box 64,%d,2,%d)",
+             (int)r, c, w, h, n, box_w, box_n);
+    return fail(buf);
+  }
+  return 0;
+}
+
+static_assert(sizeof(TensorMap) == sizeof(CUtensorMap), "tensor map size");
+
+int launch_fwd(int kind, void* out, const void* in, const void* w, const float* bias,
+               const spio_gw8_shape* sh, const spio_gw8_tune* tune, cudaStream_t stream) {
+  if (out == nullptr || in == nullptr || w == nullptr) return fail("NULL tensor pointer");
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;
+  Plan pl;
+  if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
+  const Gw8Geom& g = pl.g;
+  CUtensorMap in_map, out_map;
+  if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, g.bw, g.nb)) return 1;
+  if (encode_map(&out_map, out, g.c, g.out_w, g.out_h, g.n, g.wt, g.nb)) return 1;
+  if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
+  const __half* wp = static_cast<const __half*>(w);
+  int ns = pl.ns, nob = pl.nob;
+  int* status = d->status;
+  void* args[] = {&in_map, &out_map, (void*)&g, &wp, &bias, &ns, &nob, &status};
+  GW8_CUDA(cudaLaunchKernel(pl.v->fwd_kernel, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
+  return 0;
+}
+
+int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape* sh,
+                 const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes,
+                 cudaStream_t stream) {
+  if (dw == nullptr || x == nullptr || dy == nullptr) return fail("NULL tensor pointer");
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;
+  Plan pl;
+  if (make_plan(SPIO_GW8_WGRAD, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
+  if (scratch == nullptr || scratch_bytes < pl.scratch_bytes) return fail("wgrad scratch buffer is too small");
+  if ((reinterpret_cast<size_t>(scratch) & 15u) != 0 || (reinterpret_cast<size_t>(dw) & 15u) != 0)
+    return fail("dw and scratch must be 16-byte aligned");
+  const Gw8Geom& g = pl.g;
+  CUtensorMap x_map, dy_map;
+  if (encode_map(&x_map, x, g.c, g.in_w, g.in_h, g.n, g.bw, g.nb)) return 1;
+  if (encode_map(&dy_map, dy, g.c, g.out_w, g.out_h, g.n, g.wt, g.nb)) return 1;
+  float* sc = static_cast<float*>(scratch);
+  int ns = pl.ns;
+  int* status = d->status;
+  void* args[] = {&x_map, &dy_map, (void*)&g, &sc, &ns, &status};
+  GW8_CUDA(cudaLaunchKernel(pl.v->wgrad_kernel, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
+  const int taps = sh->r * sh->s;
+  const int total_f4 = g.c * taps * 2;
+  constexpr int RW = 16;
+  conv2d_gw8_wgrad_reduce_kernel<RW><<<cdiv(total_f4, 32), dim3(32, RW), 0, stream>>>(
+      dw, sc, g.c, taps, g.n_split * pl.v->wpg);
+  GW8_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------- host-buffer variants
+
+struct HostStage {
+  cudaStream_t stream = nullptr;
+  void* buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t cap[5] = {0, 0, 0, 0, 0};
+};
+HostStage g_stage[kMaxDevices];
+std::mutex g_stage_mutex;
+
+int stage_reserve(HostStage& st, int i, size_t bytes) {
+  if (bytes <= st.cap[i]) return 0;
+  if (st.buf[i]) GW8_CUDA(cudaFree(st.buf[i]));
+  st.buf[i] = nullptr;
+  st.cap[i] = 0;
+  GW8_CUDA(cudaMalloc(&st.buf[i], bytes));
+  st.cap[i] = bytes;
+  return 0;
+}
+
+int get_stage(HostStage** out) {
+  int dev = 0;
+  GW8_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device ordinal out of range");
+  HostStage& st = g_stage[dev];
+  if (st.stream == nullptr) GW8_CUDA(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
+  *out = &st;
+  return 0;
+}
+
+size_t act_bytes(const spio_gw8_shape* sh, bool output) {
+  const int p = sh->h + 2 * sh->pad_h - sh->r + 1;
+  const int q = sh->w + 2 * sh->pad_w - sh->s + 1;
+  return (size_t)sh->n * sh->c * (output ? (size_t)p * q : (size_t)sh->h * sh->w) * 2;
+}
+
+size_t weight_elems(const spio_gw8_shape* sh) { return (size_t)sh->c * sh->r * sh->s * 8; }
+
+void fill_info(const Plan& pl, spio_gw8_plan_info* info) {
+  info->wpg = pl.v->wpg;
+  info->tpw = pl.v->tpw;
+  info->ns = pl.ns;
+  info->nob = pl.nob;
+  info->ncb = pl.g.ncb;
+  info->nb = pl.g.nb;
+  info->grid = pl.grid;
+  info->threads = pl.threads;
+  info->smem_bytes = pl.smem;
+  info->n_chunks = pl.g.n_chunks;
+  info->n_image_groups = pl.g.n_ig;
+  info->n_col_tiles = pl.g.n_ct;
+  info->n_pairs = pl.g.n_pairs;
+  info->n_split = pl.g.n_split;
+  info->scratch_bytes = pl.scratch_bytes;
+}
+
+}  // namespace
+
+}  // namespace spio_b200
+
+using namespace spio_b200;
+
+extern "C" {
+
+int spio_conv2d_gw8_fprop(void* y, const void* x, const void* w, const float* bias,
+                          const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* stream) {
+  return launch_fwd(SPIO_GW8_FPROP, y, x, w, bias, shape, tune, (cudaStream_t)stream);
+}
+
+int spio_conv2d_gw8_dgrad(void* dx, const void* dy, const void* w, const spio_gw8_shape* shape,
+                          const spio_gw8_tune* tune, void* stream) {
+  return launch_fwd(SPIO_GW8_DGRAD, dx, dy, w, nullptr, shape, tune, (cudaStream_t)stream);
+}
+
+size_t spio_conv2d_gw8_wgrad_scratch_bytes(const spio_gw8_shape* shape, const spio_gw8_tune* tune) {
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 0;
+  Plan pl;
+  if (make_plan(SPIO_GW8_WGRAD, shape, tune, d->sms, d->smem_optin, g_variants, &pl)) return 0;
+  return pl.scratch_bytes;
+}
+
+int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape* shape,
+                          const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes,
+                          void* stream) {
+  return launch_wgrad(dw, x, dy, shape, tune, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+int spio_conv2d_gw8_fprop_host(void* y, const void* x, const void* w, const float* bias,
+                               const spio_gw8_shape* shape, const spio_gw8_tune* tune) {
+  if (check_shape(shape)) return 1;
+  std::lock_guard<std::mutex> lock(g_stage_mutex);
+  HostStage* st = nullptr;
+  if (get_stage(&st)) return 1;
+  const size_t xb = act_bytes(shape, false), yb = act_bytes(shape, true);
+  const size_t wb = weight_elems(shape) * 2, bb = (size_t)shape->c * 4;
+  if (stage_reserve(*st, 0, xb) || stage_reserve(*st, 1, yb) || stage_reserve(*st, 2, wb)) return 1;
+  if (bias && stage_reserve(*st, 3, bb)) return 1;
+  GW8_CUDA(cudaMemcpyAsync(st->buf[0], x, xb, cudaMemcpyHostToDevice, st->stream));
+  GW8_CUDA(cudaMemcpyAsync(st->buf[2], w, wb, cudaMemcpyHostToDevice, st->stream));
+  if (bias) GW8_CUDA(cudaMemcpyAsync(st->buf[3], bias, bb, cudaMemcpyHostToDevice, st->stream));
+  if (launch_fwd(SPIO_GW8_FPROP, st->buf[1], st->buf[0], st->buf[2],
+                 bias ? (const float*)st->buf[3] : nullptr, shape, tune, st->stream))
+    return 1;
+  GW8_CUDA(cudaMemcpyAsync(y, st->buf[1], yb, cudaMemcpyDeviceToHost, st->stream));
+  GW8_CUDA(cudaStreamSynchronize(st->stream));
+  return 0;
+}
+
+int spio_conv2d_gw8_dgrad_host(void* dx, const void* dy, const void* w, const spio_gw8_shape* shape,
+                               const spio_gw8_tune* tune) {
+  if (check_shape(shape)) return 1;
+  std::lock_guard<std::mutex> lock(g_stage_mutex);
+  HostStage* st = nullptr;
+  if (get_stage(&st)) return 1;
+  const size_t xb = act_bytes(shape, false), yb = act_bytes(shape, true);
+  const size_t wb = weight_elems(shape) * 2;
+  if (stage_reserve(*st, 0, xb) || stage_reserve(*st, 1, yb) || stage_reserve(*st, 2, wb)) return 1;
+  GW8_CUDA(cudaMemcpyAsync(st->buf[1], dy, yb, cudaMemcpyHostToDevice, st->stream));
+  GW8_CUDA(cudaMemcpyAsync(st->buf[2], w, wb, cudaMemcpyHostToDevice, st->stream));
+  if (launch_fwd(SPIO_GW8_DGRAD, st->buf[0], st->buf[1], st->buf[2], nullptr, shape, tune, st->stream))
+    return 1;
+  GW8_CUDA(cudaMemcpyAsync(dx, st->buf[0], xb, cudaMemcpyDeviceToHost, st->stream));
+  GW8_CUDA(cudaStreamSynchronize(st->stream));
+  return 0;
+}
+
+int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy, const spio_gw8_shape* shape,
+                               const spio_gw8_tune* tune) {
+  if (check_shape(shape)) return 1;
+  const size_t scratch = spio_conv2d_gw8_wgrad_scratch_bytes(shape, tune);
+  if (scratch == 0) return 1;
+  std::lock_guard<std::mutex> lock(g_stage_mutex);
+  HostStage* st = nullptr;
+  if (get_stage(&st)) return 1;
+  const size_t xb = act_bytes(shape, false), yb = act_bytes(shape, true);
+  const size_t wb = weight_elems(shape) * 4;
+  if (stage_reserve(*st, 0, xb) || stage_reserve(*st, 1, yb) || stage_reserve(*st, 2, wb) ||
+      stage_reserve(*st, 4, scratch))
+    return 1;
+  GW8_CUDA(cudaMemcpyAsync(st->buf[0], x, xb, cudaMemcpyHostToDevice, st->stream));
+  GW8_CUDA(cudaMemcpyAsync(st->buf[1], dy, yb, cudaMemcpyHostToDevice, st->stream));
+  if (launch_wgrad((float*)st->buf[2], st->buf[0], st->buf[1], shape, tune, st->buf[4], scratch,
+                   st->stream))
+    return 1;
+  GW8_CUDA(cudaMemcpyAsync(dw, st->buf[2], wb, cudaMemcpyDeviceToHost, st->stream));
+  GW8_CUDA(cudaStreamSynchronize(st->stream));
+  return 0;
+}
+
+int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                         spio_gw8_plan_info* info) {
+  if (info == nullptr) return fail("info is NULL");
+  if (kind < SPIO_GW8_FPROP || kind > SPIO_GW8_WGRAD) return fail("unknown kind");
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;
+  Plan pl;
+  if (make_plan(kind, shape, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
+  fill_info(pl, info);
+  return 0;
+}
+
+int spio_conv2d_gw8_plan_for(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                             int sm_count, int smem_optin_bytes, spio_gw8_plan_info* info) {
+  if (info == nullptr) return fail("info is NULL");
+  if (kind < SPIO_GW8_FPROP || kind > SPIO_GW8_WGRAD) return fail("unknown kind");
+  if (sm_count <= 0 || smem_optin_bytes <= 0) return fail("sm_count and smem_optin_bytes must be positive");
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    load_variants_locked();
+  }
+  Plan pl;
+  if (make_plan(kind, shape, tune, sm_count, smem_optin_bytes, g_variants, &pl)) return 1;
+  fill_info(pl, info);
+  return 0;
+}
+
+int spio_conv2d_gw8_num_variants(void) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  load_variants_locked();
+  return (int)g_variants.size();
+}
+
+int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  load_variants_locked();
+  if (i < 0 || i >= (int)g_variants.size()) return fail("variant index out of range");
+  if (r) *r = g_variants[i].r;
+  if (s) *s = g_variants[i].s;
+  if (wpg) *wpg = g_variants[i].wpg;
+  if (tpw) *tpw = g_variants[i].tpw;
+  return 0;
+}
+
+int spio_b200_device_status(int* status) {
+  if (status == nullptr) return fail("status is NULL");
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;
+  GW8_CUDA(cudaDeviceSynchronize());
+  GW8_CUDA(cudaMemcpy(status, d->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status != 0) GW8_CUDA(cudaMemset(d->status, 0, sizeof(int)));
+  return 0;
+}
+
+const char* spio_b200_last_error(void) { return g_last_error.c_str(); }
+
+const char* spio_b200_version(void) { return "spio_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

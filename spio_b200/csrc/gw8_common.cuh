@@ -1,0 +1,112 @@
+// Shared definitions of the group-width-8 convolution kernels: the launch-time
+// geometry, the compile-time tile configuration and the walk of a CTA over its
+// share of the work.
+//
+// Vocabulary (all sizes in output coordinates unless noted):
+//   chunk      64 consecutive channels = 8 groups of width 8; one TMA box is 64
+//              channels (128 bytes) wide and is stored with the 128-byte swizzle.
+//   pair       two consecutive output rows (2m, 2m+1).
+//   col tile   Wt = 8*ncb output columns, ncb "column blocks" of 8 pixels.
+//   image group NB consecutive images that share one box.
+//   slot       one TMA box of the streamed tensor: NB images x 2 rows x BW columns
+//              x 64 channels, BW = round_up(Wt + S - 1, 8).  Slot j of a segment
+//              holds padded rows 2j and 2j+1 (padded row = input row + pad_h).
+//   segment    a run of pairs of one (chunk, image group, col tile) that one CTA
+//              streams top to bottom, carrying its register window of input rows.
+//
+// The tiling arithmetic replaces the reference's per-shape generated index types
+// (spio/kernels/conv2d_gw8_kernel.py:62-238, conv2d_gw8_wgrad_kernel.py:92-285).
+#pragma once
+
+#include "ptx.cuh"
+
+namespace spio_b200 {
+
+// Opaque 128-byte tensor map; <cuda.h> is not includable under NVRTC.
+struct alignas(64) TensorMap {
+  unsigned long long opaque[16];
+};
+
+enum Gw8Status {
+  GW8_OK = 0,
+  GW8_WAIT_TIMEOUT = 1,  // a bounded mbarrier wait gave up
+};
+
+// Launch-time geometry.  "in" is the streamed operand with a halo (x for fprop and
+// wgrad, dy for dgrad); "out" is the tensor tiled without halo (y, dx; dy for wgrad).
+struct Gw8Geom {
+  int n, c;            // batch, channels (multiple of 8)
+  int in_h, in_w;      // streamed-operand height / width
+  int out_h, out_w;    // tiled-operand height / width
+  int pad_h, pad_w;    // zero padding of the streamed operand (may be negative)
+  int n_chunks;        // ceil(c / 64)
+  int n_ig;            // ceil(n / nb)
+  int n_ct;            // column tiles
+  int n_pairs;         // ceil(out_h / 2)
+  int ncb;             // column blocks (of 8 pixels) per column tile
+  int nb;              // images per slot
+  int wt;              // 8 * ncb
+  int bw;              // slot width in pixels, multiple of 8
+  int ntiles;          // nb * ncb  (<= WPG * TPW)
+  int dgrad;           // 1: weights are used transposed and flipped
+  int n_split;         // wgrad: CTAs that share one chunk
+};
+
+// Compile-time tile configuration.
+//   R, S   filter size;  WPG warps per group;  TPW tiles (8 px x 2 rows) per warp.
+// The number of ring slots and of output staging buffers is a launch argument.
+template <int R_, int S_, int WPG_, int TPW_>
+struct Gw8Config {
+  static constexpr int R = R_, S = S_, WPG = WPG_, TPW = TPW_;
+  static constexpr int E = R / 2;          // extra slots a pair needs below its own
+  static constexpr int WIN = 2 * E + 2;    // rows of the register window
+  static constexpr int NT = R * S;         // taps
+  static constexpr int NCW = 8 * WPG;      // consumer warps
+  static constexpr int THREADS = (NCW + 2) * 32;  // + load warp + store warp
+  static constexpr int MAX_TILES = WPG * TPW;
+};
+
+// One segment of a CTA's span.
+struct Gw8Segment {
+  int ck, ig, ct;  // chunk, image group, column tile
+  int m0, m1;      // pairs [m0, m1)
+};
+
+// Walks the span [u0, u1) of the flattened (chunk, image group, col tile, pair)
+// sequence and cuts it into segments.  Every role of a CTA (load, compute, store)
+// runs the same walk, so they agree on the order of slots without communicating.
+struct Gw8Walk {
+  int u, u1, n_pairs, n_ct, n_ig;
+
+  __device__ __forceinline__ Gw8Walk(int u0_, int u1_, const Gw8Geom& g)
+      : u(u0_), u1(u1_), n_pairs(g.n_pairs), n_ct(g.n_ct), n_ig(g.n_ig) {}
+
+  __device__ __forceinline__ bool next(Gw8Segment& s) {
+    if (u >= u1) return false;
+    int m = u % n_pairs;
+    int rest = u / n_pairs;
+    s.ct = rest % n_ct;
+    rest /= n_ct;
+    s.ig = rest % n_ig;
+    s.ck = rest / n_ig;
+    s.m0 = m;
+    int len = n_pairs - m;
+    if (len > u1 - u) len = u1 - u;
+    s.m1 = m + len;
+    u += len;
+    return true;
+  }
+};
+
+// Span of CTA `b` out of `nb` over `total` units, balanced to within one unit.
+__device__ __forceinline__ int gw8_span_begin(int total, int b, int nb) {
+  return (int)(((long long)total * b) / nb);
+}
+
+// Byte offset inside a swizzled slot of the 16-byte piece holding channels
+// [8*grp, 8*grp+8) of pixel `pix`; the slot base must be 1024-byte aligned.
+__device__ __forceinline__ u32 gw8_swizzle(u32 pix, u32 grp) {
+  return pix * 128u + ((grp ^ (pix & 7u)) << 4);
+}
+
+}  // namespace spio_b200

@@ -1,0 +1,39 @@
+// Host-side plumbing shared by the translation units of libspio_b200: the launcher
+// table filled by the per-filter-height instantiation files, and the planning of a
+// launch (tile geometry, shared-memory budget, tensor maps).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+#include "gw8_common.cuh"
+
+namespace spio_b200 {
+
+// Tile configuration requested by the caller; zero fields are chosen by the planner.
+struct Gw8Tune {
+  int wpg;  // warps per group (compiled variants only)
+  int tpw;  // tiles per warp  (compiled variants only)
+  int ns;   // ring slots
+  int nob;  // output staging buffers
+  int ncb;  // column blocks per column tile
+  int nb;   // images per slot
+  int grid; // CTAs (0: one per SM)
+};
+
+struct Gw8Variant {
+  int r, s, wpg, tpw;
+  int fwd_threads, wgrad_threads;
+  const void* fwd_kernel;    // conv2d_gw8_fwd_kernel<Cfg>
+  const void* wgrad_kernel;  // conv2d_gw8_wgrad_kernel<Cfg>
+};
+
+// Each gw8_inst.cu build (one per filter height R) exports its variants.
+int gw8_variants_r1(const Gw8Variant** out);
+int gw8_variants_r2(const Gw8Variant** out);
+int gw8_variants_r3(const Gw8Variant** out);
+int gw8_variants_r4(const Gw8Variant** out);
+int gw8_variants_r5(const Gw8Variant** out);
+
+}  // namespace spio_b200

@@ -1,0 +1,200 @@
+// Thin inline-PTX wrappers for the sm_100a building blocks the gw8 kernels use:
+// mbarrier (with time-bounded waits), TMA tiled loads/stores (never multicast),
+// ldmatrix / stmatrix and warp-level mma.sync with fp32 accumulation.
+//
+// The file is device-only and includes no host headers, so the same text compiles
+// under nvcc (ahead of time) and under NVRTC (just in time).
+//
+// Replaces the Ampere-era wrappers of the reference: spio/include/spio/memory.cuh:17-24
+// (cp.async zfill), spio/include/spio/ldmatrix.cuh:16-109, spio/include/spio/mma.cuh:33-42.
+#pragma once
+
+namespace spio_b200 {
+
+typedef unsigned int u32;
+typedef unsigned long long u64;
+
+// A wait gives up after this many nanoseconds of wall time and reports failure
+// instead of spinning for ever.
+#ifndef SPIO_WAIT_LIMIT_NS
+#define SPIO_WAIT_LIMIT_NS 2000000000ull
+#endif
+
+__device__ __forceinline__ u32 smem_u32(const void* p) {
+  return (u32)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ u64 globaltimer_ns() {
+  u64 t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// ---------------------------------------------------------------- mbarrier
+
+__device__ __forceinline__ void mbar_init(u32 bar, u32 count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(u32 bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(u32 bar, u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(u32 bar, u32 parity) {
+  u32 ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Waits for the phase with the given parity to complete.  Returns false when the
+// CTA-wide abort flag is (or becomes) set: either another thread gave up, or this
+// wait exceeded SPIO_WAIT_LIMIT_NS.  The caller must then leave its loop.
+__device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  u64 t0 = 0;
+  for (u32 it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      u64 now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > SPIO_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- TMA (tiled, 4-D)
+
+// Generic-proxy writes to shared memory (st.shared / stmatrix) become visible to
+// the async proxy (TMA store) only after this fence.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// Tiled load of one box.  The innermost coordinate c0 times the element size must
+// be a multiple of 16 bytes; the other coordinates may be negative or out of range
+// (the box is zero-filled there).
+__device__ __forceinline__ void tma_load_4d(u32 dst, const void* tmap, u32 bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Tiled store of one box; elements outside the tensor are dropped.  All coordinates
+// must be non-negative.
+__device__ __forceinline__ void tma_store_4d(const void* tmap, u32 src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group "
+      "[%0, {%2, %3, %4, %5}], [%1];" ::"l"(tmap),
+      "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// Until the shared-memory source of every committed store has been read.
+__device__ __forceinline__ void tma_store_wait_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// Until every committed store has completed.
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- ldmatrix / stmatrix
+
+// COUNT 8x8 b16 matrices; lane L supplies the row address of matrix L/8, row L%8.
+// Thread (g = L/4, t = L%4) receives elements (row g, cols 2t, 2t+1) of each matrix,
+// or with TRANS elements (rows 2t, 2t+1, col g).
+template <bool TRANS>
+__device__ __forceinline__ void ldmatrix_x4(u32& r0, u32& r1, u32& r2, u32& r3, u32 addr) {
+  if (TRANS)
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+  else
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+
+template <bool TRANS>
+__device__ __forceinline__ void ldmatrix_x2(u32& r0, u32& r1, u32 addr) {
+  if (TRANS)
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"(addr));
+  else
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"(addr));
+}
+
+template <bool TRANS>
+__device__ __forceinline__ void ldmatrix_x1(u32& r0, u32 addr) {
+  if (TRANS)
+    asm volatile("ldmatrix.sync.aligned.m8n8.x1.trans.shared.b16 {%0}, [%1];"
+                 : "=r"(r0)
+                 : "r"(addr));
+  else
+    asm volatile("ldmatrix.sync.aligned.m8n8.x1.shared.b16 {%0}, [%1];" : "=r"(r0) : "r"(addr));
+}
+
+__device__ __forceinline__ void stmatrix_x2(u32 addr, u32 r0, u32 r1) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x2.shared.b16 [%0], {%1,%2};" ::"r"(addr), "r"(r0),
+               "r"(r1)
+               : "memory");
+}
+
+// ---------------------------------------------------------------- mma.sync (fp16 x fp16 -> fp32)
+
+// D(16x8) += A(16x16) * B(16x8).  a0:(rows 0-7,k 0-7) a1:(rows 8-15,k 0-7)
+// a2:(rows 0-7,k 8-15) a3:(rows 8-15,k 8-15); b0: k 0-7, b1: k 8-15.
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], u32 a0, u32 a1, u32 a2, u32 a3, u32 b0,
+                                             u32 b1) {
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D(16x8) += A(16x8) * B(8x8).
+__device__ __forceinline__ void mma_m16n8k8(float (&d)[4], u32 a0, u32 a1, u32 b0) {
+  asm(
+      "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0));
+}
+
+}  // namespace spio_b200
