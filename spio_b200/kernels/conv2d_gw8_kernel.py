@@ -1,0 +1,108 @@
+"""Forward / input-gradient kernel family: tile configurations and the kernel factory.
+
+Counterpart of the reference's spio/kernels/conv2d_gw8_kernel.py:30-238.  A configuration
+there fixes (groups per CTA, block_p, block_n) of a one-tile-per-CTA kernel; here the
+kernel is persistent and streams row pairs through a shared-memory ring, so a
+configuration fixes the warp mapping and the ring instead:
+
+    wpg  compute warps per channel group        tpw  8-pixel x 2-row tiles per warp
+    ncb  8-pixel column blocks per column tile   nb   images per ring slot
+    ns   ring slots                              nob  output staging buffers
+
+A zero means "let the launch planner choose".
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import asdict, dataclass
+from typing import Iterator, List
+
+from .. import _clib
+from ..util.math import divup
+from .conv2d_gw8_params import Conv2dGw8Params
+from .conv2d_stats import Conv2dStats
+from .kernel import shape_of
+from .kernel_factory import KernelFactory
+
+
+@dataclass(frozen=True)
+class Conv2dGw8Config:
+    wpg: int = 0
+    tpw: int = 0
+    ncb: int = 0
+    nb: int = 0
+    ns: int = 0
+    nob: int = 0
+
+    def as_tune(self) -> dict:
+        return asdict(self)
+
+
+def compiled_variants(r: int, s: int) -> List[tuple]:
+    """(wpg, tpw) pairs compiled into the library for an r x s filter."""
+    lib = _clib.load()
+    out = []
+    vr, vs, vw, vt = (ctypes.c_int() for _ in range(4))
+    for i in range(lib.spio_conv2d_gw8_num_variants()):
+        lib.spio_conv2d_gw8_variant(i, ctypes.byref(vr), ctypes.byref(vs), ctypes.byref(vw),
+                                    ctypes.byref(vt))
+        if (vr.value, vs.value) == (r, s):
+            out.append((vw.value, vt.value))
+    return out
+
+
+def plan_is_valid(kind: int, params, tune: dict, device_attr) -> bool:
+    lib = _clib.load()
+    info = _clib.PlanInfo()
+    t = _clib.make_tune(tune)
+    rc = lib.spio_conv2d_gw8_plan_for(kind, ctypes.byref(shape_of(params)), ctypes.byref(t),
+                                      device_attr.multiprocessor_count,
+                                      device_attr.max_shared_memory_per_block_optin,
+                                      ctypes.byref(info))
+    return rc == 0
+
+
+def enumerate_tiles(params, out_w: int, wpg: int, tpw: int) -> Iterator[tuple]:
+    """(ncb, nb) candidates: the width cut into 1..4 column tiles; several images per slot
+    only when one tile spans the whole width."""
+    max_tiles = wpg * tpw
+    col_blocks = divup(out_w, 8)
+    seen = set()
+    for n_ct in range(1, 5):
+        ncb = divup(col_blocks, n_ct)
+        if ncb > max_tiles or ncb in seen:
+            continue
+        seen.add(ncb)
+        yield ncb, 1
+        if ncb >= col_blocks:
+            nb = 2
+            while nb * ncb <= max_tiles and nb <= params.n:
+                yield ncb, nb
+                nb *= 2
+
+
+def _get_configs(params: Conv2dGw8Params, device_attr, igrad: bool = False) -> Iterator[Conv2dGw8Config]:
+    kind = _clib.DGRAD if igrad else _clib.FPROP
+    out_w = params.w if igrad else params.q
+    for wpg, tpw in compiled_variants(params.r, params.s):
+        for ncb, nb in enumerate_tiles(params, out_w, wpg, tpw):
+            for ns in (0, 4, 6, 8):
+                for nob in (2, 3):
+                    cfg = Conv2dGw8Config(wpg=wpg, tpw=tpw, ncb=ncb, nb=nb, ns=ns, nob=nob)
+                    if plan_is_valid(kind, params, cfg.as_tune(), device_attr):
+                        yield cfg
+
+
+def _get_kernel_name(igrad: bool = False) -> str:
+    return "spio_conv2d_gw8_dgrad" if igrad else "spio_conv2d_gw8_fprop"
+
+
+conv2d_gw8_kernel_factory = KernelFactory(
+    Conv2dGw8Params,
+    Conv2dGw8Config,
+    Conv2dStats,
+    kernel_name=_get_kernel_name,
+    configs=_get_configs,
+    perf_model_skip_params=["group_width", "stride"],
+)

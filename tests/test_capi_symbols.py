@@ -1,0 +1,94 @@
+"""The C-ABI library loads without a GPU, exports every symbol include/spio_b200.h declares,
+and its device-free planner produces launches that respect the hardware limits."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from spio_b200 import _clib
+from tests.shapes import REFERENCE_TEST_SHAPES, ident
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "spio_b200.h"
+SMS, SMEM = 148, 232448
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(spio_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    lib = _clib.load()
+    names = declared_functions()
+    assert len(names) >= 14
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert set(names) == set(_clib.SIGNATURES), "ctypes binding out of step with the header"
+    assert b"sm_100a" in lib.spio_b200_version()
+
+
+def test_struct_layouts_match_the_header():
+    assert ctypes.sizeof(_clib.Shape) == 8 * 4
+    assert ctypes.sizeof(_clib.Tune) == 7 * 4
+    assert ctypes.sizeof(_clib.PlanInfo) == 14 * 4 + 8
+
+
+def plan(kind, sh, tune=None):
+    lib = _clib.load()
+    info = _clib.PlanInfo()
+    s = _clib.Shape(sh.n, sh.c, sh.h, sh.w, sh.r, sh.s, sh.pad_h, sh.pad_w)
+    rc = lib.spio_conv2d_gw8_plan_for(kind, ctypes.byref(s), _clib.tune_ref(tune), SMS, SMEM,
+                                      ctypes.byref(info))
+    return rc, info.as_dict()
+
+
+@pytest.mark.parametrize("case", REFERENCE_TEST_SHAPES, ids=ident)
+@pytest.mark.parametrize("kind", [_clib.FPROP, _clib.DGRAD, _clib.WGRAD])
+def test_planner_respects_limits(case, kind):
+    sh, _ = case
+    rc, p = plan(kind, sh)
+    assert rc == 0, _clib.last_error()
+    assert 1 <= p["grid"] <= SMS
+    assert p["smem_bytes"] <= SMEM - 512
+    assert p["nb"] * p["ncb"] <= p["wpg"] * p["tpw"]
+    assert p["ns"] >= sh.r // 2 + 2
+    assert p["threads"] % 32 == 0 and p["threads"] <= 1024
+    out_w = sh.w if kind == _clib.DGRAD else sh.q
+    out_h = sh.h if kind == _clib.DGRAD else sh.p
+    assert p["n_col_tiles"] * p["ncb"] * 8 >= out_w
+    assert p["n_pairs"] * 2 >= out_h
+    assert p["n_image_groups"] * p["nb"] >= sh.n
+    assert p["n_chunks"] * 64 >= sh.c
+    if kind == _clib.WGRAD:
+        assert p["scratch_bytes"] == p["n_chunks"] * p["n_split"] * p["wpg"] * 64 * sh.r * sh.s * 8 * 4
+        assert p["grid"] == (p["n_split"] * p["n_chunks"] if p["n_chunks"] <= SMS else SMS)
+    else:
+        assert p["scratch_bytes"] == 0
+
+
+def test_planner_rejects_bad_requests():
+    from oracle.oracle import Shape
+
+    lib = _clib.load()
+    rc, _ = plan(_clib.FPROP, Shape(1, 12, 8, 8))
+    assert rc != 0 and "divisible by group width" in _clib.last_error()
+    rc, _ = plan(_clib.FPROP, Shape(1, 16, 8, 8, 6, 3))
+    assert rc != 0 and "between 1 and 5" in _clib.last_error()
+    rc, _ = plan(_clib.FPROP, Shape(1, 16, 2, 2, 5, 5, 0, 0))
+    assert rc != 0 and "positive" in _clib.last_error()
+    rc, _ = plan(_clib.FPROP, Shape(1, 16, 8, 8), dict(wpg=7))
+    assert rc != 0 and "variant" in _clib.last_error()
+    rc, _ = plan(_clib.FPROP, Shape(1, 64, 56, 56), dict(ns=16, nob=4))
+    assert rc != 0 and "shared memory" in _clib.last_error()
+    assert lib.spio_conv2d_gw8_plan_for(9, None, None, SMS, SMEM, None) != 0
+
+
+def test_headline_plan():
+    from oracle.oracle import Shape
+
+    rc, p = plan(_clib.FPROP, Shape(2048, 64, 56, 56))
+    assert rc == 0 and p["grid"] == 148 and p["ncb"] == 7 and p["nb"] == 1 and p["n_pairs"] == 28
+    rc, p = plan(_clib.WGRAD, Shape(2048, 64, 56, 56))
+    assert rc == 0 and p["n_split"] == 148 and p["grid"] == 148
