@@ -128,7 +128,8 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    n = GLOBAL_BATCH // world
+    global_batch = args.global_batch
+    n = global_batch // world
     lib = _clib.load()
     sh = _clib.Shape(n, C, H, W, R, S, PAD, PAD)
     shp = ctypes.byref(sh)
@@ -208,32 +209,34 @@ def run_ours(args) -> None:
     kern_ms = [statistics.fmean(e[i].elapsed_time(e[i + 1]) for e in evs) for i in range(3)]
 
     # ---- end to end through the host-buffer C ABI: pinned host operands, H2D + D2H inside
-    e2e_steps = min(args.steps, 3)
+    e2e_steps = 0 if args.no_e2e else min(args.steps, 3)
     act_bytes = n * C * H * W * 2
-    hx = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
-    hdy = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
-    hy = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
-    hdx = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
-    hw = torch.empty(C, R, S, 8, dtype=torch.float16).pin_memory()
-    hdw = torch.empty(C, R, S, 8, dtype=torch.float32).pin_memory()
-    hx.copy_(x.permute(0, 2, 3, 1))
-    hdy.copy_(dy.permute(0, 2, 3, 1))
-    hw.copy_(w.permute(0, 2, 3, 1))
+    e2e_s, e2e_ok = float("nan"), None
+    if e2e_steps:
+        hx = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
+        hdy = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
+        hy = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
+        hdx = torch.empty(n, H, W, C, dtype=torch.float16).pin_memory()
+        hw = torch.empty(C, R, S, 8, dtype=torch.float16).pin_memory()
+        hdw = torch.empty(C, R, S, 8, dtype=torch.float32).pin_memory()
+        hx.copy_(x.permute(0, 2, 3, 1))
+        hdy.copy_(dy.permute(0, 2, 3, 1))
+        hw.copy_(w.permute(0, 2, 3, 1))
 
-    def e2e_step():
-        _clib.check(lib.spio_conv2d_gw8_fprop_host(hy.data_ptr(), hx.data_ptr(), hw.data_ptr(), None, shp, None))
-        _clib.check(lib.spio_conv2d_gw8_wgrad_host(hdw.data_ptr(), hx.data_ptr(), hdy.data_ptr(), shp, None))
-        _clib.check(lib.spio_conv2d_gw8_dgrad_host(hdx.data_ptr(), hdy.data_ptr(), hw.data_ptr(), shp, None))
+        def e2e_step():
+            _clib.check(lib.spio_conv2d_gw8_fprop_host(hy.data_ptr(), hx.data_ptr(), hw.data_ptr(), None, shp, None))
+            _clib.check(lib.spio_conv2d_gw8_wgrad_host(hdw.data_ptr(), hx.data_ptr(), hdy.data_ptr(), shp, None))
+            _clib.check(lib.spio_conv2d_gw8_dgrad_host(hdx.data_ptr(), hdy.data_ptr(), hw.data_ptr(), shp, None))
 
-    e2e_step()
-    barrier()
-    w0 = time.perf_counter()
-    for _ in range(e2e_steps):
         e2e_step()
-    barrier()
-    e2e_s = (time.perf_counter() - w0) / e2e_steps
-    # the host-buffer result must equal the device-pointer result bit for bit
-    e2e_ok = bool(torch.equal(hy[:2], y[:2].permute(0, 2, 3, 1).cpu()))
+        barrier()
+        w0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = (time.perf_counter() - w0) / e2e_steps
+        # the host-buffer result must equal the device-pointer result bit for bit
+        e2e_ok = bool(torch.equal(hy[:2], y[:2].permute(0, 2, 3, 1).cpu()))
 
     times = torch.tensor([total_ms, e2e_s * 1e3] + kern_ms, device=dev, dtype=torch.float64)
     if world > 1:
@@ -244,10 +247,11 @@ def run_ours(args) -> None:
         ms_per_step = total_ms / args.steps
         b_one = algorithmic_bytes(n)
         step_bytes_all = 3 * b_one * world
+        GB = global_batch
         peak, peak_kind = measured_peak()
         achieved = b_one / (k_fprop * 1e-3) / 1e9
         wl = (f"cfg5 DP gw8 train step: C=K=64 56x56 3x3 pad1 gw8 fp16 NHWC, global batch "
-              f"{GLOBAL_BATCH} sharded over {world} GPU(s) ({n}/rank); fprop+wgrad+dgrad"
+              f"{GB} sharded over {world} GPU(s) ({n}/rank); fprop+wgrad+dgrad"
               + (", 1 NCCL all-reduce of dw overlapped with dgrad" if world > 1 else ""))
         line = {
             "metric": "gw8 conv fprop+dgrad+wgrad effective bandwidth (algorithmic bytes / device time)",
@@ -262,10 +266,10 @@ def run_ours(args) -> None:
             "vs_baseline": None,
             "dtype": "f16 operands, f32 accumulate",
             "data": "synthetic",
-            "config": {"workload": wl, "global_batch": GLOBAL_BATCH, "per_rank_batch": n,
+            "config": {"workload": wl, "global_batch": GB, "per_rank_batch": n,
                        "l2": "every streamed operand > L2 (126 MB); no flush between steps",
                        "parallelism": f"dp{world}"},
-            "images_per_s": GLOBAL_BATCH / (ms_per_step * 1e-3),
+            "images_per_s": GB / (ms_per_step * 1e-3),
             "frac_of_8TBps_nominal": step_bytes_all / world / (ms_per_step * 1e-3) / 1e9 / 8000.0,
             "kernels": {
                 name: {"ms": ms, "GBps": b_one / (ms * 1e-3) / 1e9, "frac_of_measured_peak": b_one / (ms * 1e-3) / 1e9 / peak}
@@ -276,7 +280,7 @@ def run_ours(args) -> None:
                          "unit": "GB/s", "frac": achieved / peak,
                          "traffic": (FWD_DRAM_TRAFFIC_RATIO * b_one if FWD_DRAM_TRAFFIC_RATIO else None),
                          "algorithmic_bytes_per_launch": b_one},
-            "e2e": {"value": step_bytes_all / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+            "e2e": None if not e2e_steps else {"value": step_bytes_all / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": 4 * act_bytes + 2 * C * R * S * 8 * 2,
                     "d2h_bytes_per_step": 2 * act_bytes + C * R * S * 8 * 4,
@@ -363,6 +367,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                    help="images over all ranks (default: the 2048 of the data-parallel sweep)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

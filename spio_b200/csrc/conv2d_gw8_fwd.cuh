@@ -108,30 +108,33 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
     }
   } else if (warp == NCW + 1) {
     // ------------------------------------------------------------ store warp
-    if (lane == 0) {
+    // Lane i owns staging buffer i: it waits until the compute warps have filled it,
+    // issues the TMA store and releases the buffer once the store has read it.  Bulk
+    // groups are tracked per thread, so the buffers drain independently.
+    if (lane < nob) {
       prefetch_tensormap(&out_map);
       Gw8Walk walk(u0, u1, g);
       Gw8Segment seg;
-      int ob = 0;
-      u32 opar = 0;
+      int turn = 0;   // which buffer the next pair goes to
+      u32 opar = 0;   // parity of this lane's next use of its buffer
       bool ok = true;
       while (ok && walk.next(seg)) {
         const int c0 = seg.ck * 64;
         const int w0 = seg.ct * g.wt;
         const int n0 = seg.ig * g.nb;
         for (int m = seg.m0; m < seg.m1; ++m) {
-          if (!mbar_wait(ofull(ob), opar, abortp)) {
-            ok = false;
-            break;
-          }
-          tma_store_4d(&out_map, obufs + (u32)ob * obuf_bytes, c0, w0, 2 * m, n0);
-          tma_store_commit();
-          tma_store_wait_read0();
-          mbar_arrive(oempty(ob));
-          if (++ob == nob) {
-            ob = 0;
+          if (turn == lane) {
+            if (!mbar_wait(ofull(lane), opar, abortp)) {
+              ok = false;
+              break;
+            }
+            tma_store_4d(&out_map, obufs + (u32)lane * obuf_bytes, c0, w0, 2 * m, n0);
+            tma_store_commit();
+            tma_store_wait_read0();
+            mbar_arrive(oempty(lane));
             opar ^= 1u;
           }
+          if (++turn == nob) turn = 0;
         }
       }
       tma_store_wait_all();

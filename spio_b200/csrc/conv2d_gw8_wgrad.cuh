@@ -244,16 +244,23 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
   }
 }
 
-// dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], parts added
-// in index order.  blockDim = (32, RW): lanes run over float4 columns, warps over parts.
-template <int RW>
-__global__ void __launch_bounds__(32 * RW)
+// dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], added in a
+// fixed order.  A block of 256 threads owns 8 float4 columns of dw; thread (cx, q) adds
+// the parts q, q+32, ... of column cx, then the 32 partial sums of a column are combined
+// by two shuffle steps and a pass over shared memory.  Launch with 256 threads and
+// grid = ceil(c * taps * 2 / 8).
+template <int THREADS = 256>
+__global__ void __launch_bounds__(THREADS)
 conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__ scratch, int c,
                                int taps, int n_parts) {
-  __shared__ float4 red[RW][32];
-  const int chunk_f4 = 64 * taps * 8 / 4;        // float4 per chunk
-  const int total_f4 = c * taps * 8 / 4;         // float4 in dw
-  const int col = blockIdx.x * 32 + threadIdx.x;  // float4 index into dw
+  __shared__ float4 red[8][8];
+  const int cx = threadIdx.x & 7;
+  const int pl = (threadIdx.x >> 3) & 3;
+  const int wy = threadIdx.x >> 5;
+  const int q = wy * 4 + pl;
+  const int chunk_f4 = 64 * taps * 8 / 4;  // float4 per chunk
+  const int total_f4 = c * taps * 8 / 4;   // float4 in dw
+  const int col = blockIdx.x * 8 + cx;
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
   if (col < total_f4) {
     const int ck = col / chunk_f4;
@@ -261,20 +268,27 @@ conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__
     const float4* src =
         reinterpret_cast<const float4*>(scratch) + (size_t)ck * n_parts * chunk_f4 + e;
 #pragma unroll 4
-    for (int p = threadIdx.y; p < n_parts; p += RW) {
-      const float4 v = src[(size_t)p * chunk_f4];
+    for (int p = q; p < n_parts; p += 32) {
+      const float4 v = __ldcg(src + (size_t)p * chunk_f4);
       sum.x += v.x;
       sum.y += v.y;
       sum.z += v.z;
       sum.w += v.w;
     }
   }
-  red[threadIdx.y][threadIdx.x] = sum;
-  __syncthreads();
-  if (threadIdx.y == 0 && col < total_f4) {
 #pragma unroll
-    for (int w = 1; w < RW; ++w) {
-      const float4 v = red[w][threadIdx.x];
+  for (int d = 8; d <= 16; d <<= 1) {
+    sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
+    sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
+    sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
+    sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
+  }
+  if (pl == 0) red[wy][cx] = sum;
+  __syncthreads();
+  if (wy == 0 && pl == 0 && col < total_f4) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+      const float4 v = red[w][cx];
       sum.x += v.x;
       sum.y += v.y;
       sum.z += v.z;

@@ -86,6 +86,10 @@ int device_info(const DeviceInfo** out) {
   int dev = 0;
   GW8_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail("device ordinal out of range");
+  // Tensor maps are encoded through the driver API, which needs the device's primary
+  // context current on the calling thread; a thread that has only inherited the runtime's
+  // device choice (an autograd worker, say) may not have it bound yet.
+  GW8_CUDA(cudaSetDevice(dev));
   std::lock_guard<std::mutex> lock(g_mutex);
   load_variants_locked();
   DeviceInfo& d = g_devices[dev];
@@ -328,9 +332,8 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
   GW8_CUDA(cudaLaunchKernel(pl.v->wgrad_kernel, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
   const int taps = sh->r * sh->s;
   const int total_f4 = g.c * taps * 2;
-  constexpr int RW = 16;
-  conv2d_gw8_wgrad_reduce_kernel<RW><<<cdiv(total_f4, 32), dim3(32, RW), 0, stream>>>(
-      dw, sc, g.c, taps, g.n_split * pl.v->wpg);
+  conv2d_gw8_wgrad_reduce_kernel<256><<<cdiv(total_f4, 8), 256, 0, stream>>>(dw, sc, g.c, taps,
+                                                                       g.n_split * pl.v->wpg);
   GW8_CUDA(cudaGetLastError());
   return 0;
 }

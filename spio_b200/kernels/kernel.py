@@ -116,7 +116,7 @@ class Kernel:
                                                          scratch.data_ptr(), self._scratch_bytes, stream)
             _clib.check(rc)
         except Exception as exc:
-            raise ValueError(f"Error in kernel {self}") from exc
+            raise ValueError(f"Error in kernel {self}: {exc}") from exc
 
     __call__ = launch
 
