@@ -42,12 +42,13 @@ typedef struct spio_gw8_tune {
   int ncb;   /* 8-pixel column blocks per column tile */
   int nb;    /* images per ring slot */
   int grid;  /* CTAs; 0 = one per SM */
+  int pps;   /* row pairs per ring slot: 1 or 2 */
 } spio_gw8_tune;
 
 /* What a launch will look like; filled by spio_conv2d_gw8_plan. */
 typedef struct spio_gw8_plan_info {
   int wpg, tpw, ns, nob, ncb, nb, grid, threads;
-  int smem_bytes;
+  int pps, smem_bytes;
   int n_chunks, n_image_groups, n_col_tiles, n_pairs, n_split;
   size_t scratch_bytes; /* wgrad only */
 } spio_gw8_plan_info;
@@ -105,9 +106,9 @@ int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_t
 int spio_conv2d_gw8_plan_for(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
                              int sm_count, int smem_optin_bytes, spio_gw8_plan_info* info);
 
-/* Number of compiled (r, s, wpg, tpw) variants, and the i-th one. */
+/* Number of compiled (r, s, wpg, tpw, pps) variants, and the i-th one. */
 int spio_conv2d_gw8_num_variants(void);
-int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw);
+int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw, int* pps);
 
 /* Kernels record a bounded wait that gave up in a per-device status word.  This call
  * synchronises the current device, returns the word through *status (0 = ok) and clears

@@ -26,7 +26,7 @@ class Shape(Structure):
 class Tune(Structure):
     """struct spio_gw8_tune; zero fields are chosen by the library."""
 
-    _fields_ = [(k, c_int) for k in ("wpg", "tpw", "ns", "nob", "ncb", "nb", "grid")]
+    _fields_ = [(k, c_int) for k in ("wpg", "tpw", "ns", "nob", "ncb", "nb", "grid", "pps")]
 
 
 class PlanInfo(Structure):
@@ -35,7 +35,7 @@ class PlanInfo(Structure):
     _fields_ = [
         (k, c_int)
         for k in (
-            "wpg", "tpw", "ns", "nob", "ncb", "nb", "grid", "threads", "smem_bytes",
+            "wpg", "tpw", "ns", "nob", "ncb", "nb", "grid", "threads", "pps", "smem_bytes",
             "n_chunks", "n_image_groups", "n_col_tiles", "n_pairs", "n_split",
         )
     ] + [("scratch_bytes", c_size_t)]
@@ -65,7 +65,7 @@ SIGNATURES = {
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),
     "spio_conv2d_gw8_num_variants": (c_int, []),
     "spio_conv2d_gw8_variant": (
-        c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
+        c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
     "spio_b200_device_status": (c_int, [POINTER(c_int)]),
     "spio_b200_last_error": (c_char_p, []),
     "spio_b200_version": (c_char_p, []),

@@ -11,12 +11,15 @@
 //
 //   * one persistent CTA per SM streams its share of output row pairs top to bottom;
 //   * a load warp feeds a ring of shared-memory slots with TMA (128-byte swizzle, halo
-//     and zero padding come from the out-of-range fill of the tiled copy);
+//     and zero padding come from the out-of-range fill of the tiled copy); a slot holds
+//     PPS row pairs, so one barrier hand-off is amortised over 2*PPS image rows;
 //   * 8*WPG compute warps (one group of 8 channels each) read every slot exactly once
 //     with ldmatrix, keep a window of WIN input rows x S column shifts in registers and
-//     issue mma.sync m16n8k16 with the two k-halves fed by two different filter taps;
-//   * results are staged with stmatrix in swizzled shared memory and written by a
-//     store warp with TMA, so every global access is a full 128-byte line.
+//     issue mma.sync m16n8k16 (M = 16 pixels of one row) with the two k-halves fed by two
+//     horizontally adjacent filter taps;
+//   * results are staged with stmatrix in swizzled shared memory and written by the
+//     lanes of a store warp with TMA, so every global access is a full 128-byte line;
+//   * barrier polls are issued ahead of the work that hides their latency.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -25,31 +28,25 @@
 
 namespace spio_b200 {
 
-template <int V>
-struct IntC {
-  static constexpr int value = V;
-};
-
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
                       const __grid_constant__ TensorMap out_map, const Gw8Geom g,
                       const __half* __restrict__ wgt, const float* __restrict__ bias,
                       int ns, int nob, int* __restrict__ status) {
-  constexpr int R = Cfg::R, S = Cfg::S, WPG = Cfg::WPG, TPW = Cfg::TPW;
+  constexpr int S = Cfg::S, WPG = Cfg::WPG, TPW = Cfg::TPW, PPS = Cfg::PPS;
   constexpr int E = Cfg::E, WIN = Cfg::WIN, NT = Cfg::NT, NCW = Cfg::NCW;
-  constexpr int NPH = WIN / 2;  // the window rotates by one slot (2 rows) per stage
+  constexpr int NPH = WIN / 2;  // the window rotates by one row pair per sub-step
   constexpr int MAX_NS = 16, MAX_NOB = 4;
 
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) u64 bars[2 * MAX_NS + 2 * MAX_NOB];
+  __shared__ Gw8StageDesc desc[MAX_NS];
   __shared__ int abort_flag;
 
-  const u32 base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const u32 slot_bytes = (u32)(g.nb * 2 * g.bw) * 128u;
-  const u32 obuf_bytes = (u32)(g.nb * 2 * g.wt) * 128u;
-  const u32 ring = base;
-  const u32 obufs = base + (u32)ns * slot_bytes;
+  // ring slots: [nb][2*PPS rows][bw][64 ch]; staging buffers: PPS x [nb][2 rows][wt][64 ch]
+  const u32 ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const u32 obufs = ring + (u32)ns * g.slot_bytes;
   const u32 bar0 = smem_u32(bars);
   auto full = [&](int i) { return bar0 + 8u * (u32)i; };
   auto empty = [&](int i) { return bar0 + 8u * (u32)(MAX_NS + i); };
@@ -70,125 +67,261 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
   }
   __syncthreads();
 
-  const int total = g.n_chunks * g.n_ig * g.n_ct * g.n_pairs;
-  const int u0 = gw8_span_begin(total, blockIdx.x, gridDim.x);
-  const int u1 = gw8_span_begin(total, blockIdx.x + 1, gridDim.x);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile int* abortp = &abort_flag;
 
-  if (warp == NCW) {
-    // ------------------------------------------------------------ load warp
-    if (lane == 0) {
-      prefetch_tensormap(&in_map);
-      Gw8Walk walk(u0, u1, g);
-      Gw8Segment seg;
-      int slot = 0;
-      u32 par = 0;
-      bool ok = true;
-      while (ok && walk.next(seg)) {
-        const int nst = seg.m1 - seg.m0 + E;
-        const int c0 = seg.ck * 64;
-        const int w0 = seg.ct * g.wt - g.pad_w;
-        const int n0 = seg.ig * g.nb;
-        for (int j = 0; j < nst; ++j) {
-          if (!mbar_wait(empty(slot), par ^ 1u, abortp)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive_expect_tx(full(slot), slot_bytes);
-          tma_load_4d(ring + (u32)slot * slot_bytes, &in_map, full(slot), c0, w0,
-                      2 * (seg.m0 + j) - g.pad_h, n0);
-          if (++slot == ns) {
-            slot = 0;
-            par ^= 1u;
-          }
-        }
-      }
+  // A segment of L pairs is streamed in ceil((L + E) / PPS) stages.  Stage i brings the
+  // input row pairs PPS*i .. PPS*i+PPS-1 (relative to the segment) and completes the
+  // output pairs PPS*i+u-E, u < PPS, that lie in [0, L).  The load warp and the store
+  // lanes walk the CTA's span; the compute warps are told what a slot holds by the
+  // descriptor the load warp writes next to it.
+  auto stages_of = [&](const Gw8Segment& sg) { return (sg.m1 - sg.m0 + E + PPS - 1) / PPS; };
+  auto out_mask = [&](int i, int len) {
+    int m = 0;
+#pragma unroll
+    for (int u = 0; u < PPS; ++u) {
+      const int q = PPS * i + u - E;
+      if (q >= 0 && q < len) m |= 1 << u;
     }
-  } else if (warp == NCW + 1) {
-    // ------------------------------------------------------------ store warp
-    // Lane i owns staging buffer i: it waits until the compute warps have filled it,
-    // issues the TMA store and releases the buffer once the store has read it.  Bulk
-    // groups are tracked per thread, so the buffers drain independently.
-    if (lane < nob) {
-      prefetch_tensormap(&out_map);
-      Gw8Walk walk(u0, u1, g);
-      Gw8Segment seg;
-      int turn = 0;   // which buffer the next pair goes to
-      u32 opar = 0;   // parity of this lane's next use of its buffer
-      bool ok = true;
-      while (ok && walk.next(seg)) {
-        const int c0 = seg.ck * 64;
-        const int w0 = seg.ct * g.wt;
-        const int n0 = seg.ig * g.nb;
-        for (int m = seg.m0; m < seg.m1; ++m) {
-          if (turn == lane) {
-            if (!mbar_wait(ofull(lane), opar, abortp)) {
+    return m;
+  };
+
+  if (warp >= NCW) {
+    const int total = g.n_chunks * g.n_ig * g.n_ct * g.n_pairs;
+    const int u0 = gw8_span_begin(total, blockIdx.x, gridDim.x);
+    const int u1 = gw8_span_begin(total, blockIdx.x + 1, gridDim.x);
+    if (warp == NCW) {
+      // ---------------------------------------------------------- load warp
+      if (lane == 0) {
+        prefetch_tensormap(&in_map);
+        Gw8Walk walk(u0, u1, g);
+        Gw8Segment seg;
+        int slot = 0;
+        u32 par = 0;
+        bool ok = true;
+        while (ok && walk.next(seg)) {
+          const int nst = stages_of(seg);
+          const int len = seg.m1 - seg.m0;
+          const int c0 = seg.ck * 64;
+          const int w0 = seg.ct * g.wt - g.pad_w;
+          const int n0 = seg.ig * g.nb;
+          for (int i = 0; i < nst; ++i) {
+            if (!mbar_wait(empty(slot), par ^ 1u, abortp)) {
               ok = false;
               break;
             }
-            tma_store_4d(&out_map, obufs + (u32)lane * obuf_bytes, c0, w0, 2 * m, n0);
-            tma_store_commit();
-            tma_store_wait_read0();
-            mbar_arrive(oempty(lane));
-            opar ^= 1u;
+            desc[slot].ck = seg.ck;
+            desc[slot].mask = out_mask(i, len);
+            desc[slot].ph0 = (PPS * i) % NPH;
+            desc[slot].flags = 0;
+            mbar_arrive_expect_tx(full(slot), g.slot_bytes);
+            tma_load_4d(ring + (u32)slot * g.slot_bytes, &in_map, full(slot), c0, w0,
+                        2 * (seg.m0 + PPS * i) - g.pad_h, n0);
+            if (++slot == ns) {
+              slot = 0;
+              par ^= 1u;
+            }
           }
-          if (++turn == nob) turn = 0;
+        }
+        if (ok && mbar_wait(empty(slot), par ^ 1u, abortp)) {
+          desc[slot].flags = GW8_STAGE_END;
+          mbar_arrive(full(slot));
         }
       }
-      tma_store_wait_all();
+    } else {
+      // ---------------------------------------------------------- store warp
+      // Lane i owns staging buffer i: it waits until the compute warps have filled it,
+      // issues the TMA stores of the stage and releases the buffer once they have read
+      // it.  Bulk groups are tracked per thread, so the buffers drain independently.
+      if (lane < nob) {
+        prefetch_tensormap(&out_map);
+        Gw8Walk walk(u0, u1, g);
+        Gw8Segment seg;
+        int turn = 0;  // which buffer the next stage goes to
+        u32 opar = 0;  // parity of this lane's next use of its buffer
+        bool ok = true;
+        while (ok && walk.next(seg)) {
+          const int nst = stages_of(seg);
+          const int len = seg.m1 - seg.m0;
+          const int c0 = seg.ck * 64;
+          const int w0 = seg.ct * g.wt;
+          const int n0 = seg.ig * g.nb;
+          for (int i = 0; i < nst; ++i) {
+            const int mask = out_mask(i, len);
+            if (mask == 0) continue;
+            if (turn == lane) {
+              if (!mbar_wait(ofull(lane), opar, abortp)) {
+                ok = false;
+                break;
+              }
+#pragma unroll
+              for (int u = 0; u < PPS; ++u) {
+                if (mask & (1 << u))
+                  tma_store_4d(&out_map,
+                               obufs + (u32)lane * g.obuf_bytes + (u32)u * g.out_pair_bytes, c0, w0,
+                               2 * (seg.m0 + PPS * i + u - E), n0);
+              }
+              tma_store_commit();
+              tma_store_wait_read0();
+              mbar_arrive(oempty(lane));
+              opar ^= 1u;
+            }
+            if (++turn == nob) turn = 0;
+          }
+        }
+        tma_store_wait_all();
+      }
     }
   } else {
     // ------------------------------------------------------------ compute warps
+    // A warp owns one channel group and TPW "block tiles": 16 consecutive pixels of the
+    // rows of one image.  For each input row and each pair of column shifts (s, s+1) ONE
+    // ldmatrix.x4 delivers {shift s: px 0-7, px 8-15; shift s+1: px 0-7, px 8-15}, which is
+    // exactly the A operand of an m16n8k16 whose k-halves are the taps (r,s) and (r,s+1);
+    // an odd last shift comes from an .x2 and feeds an m16n8k8.  Operands therefore sit in
+    // consecutive registers as the hardware wants them: no register moves.
     const int grp = warp & 7;
     const int wsub = warp >> 3;
     const u32 l7 = lane & 7;
-    const int gq = lane >> 2;  // fragment row / column index "g"
-    const int t4 = lane & 3;   // fragment pair index "t"
+    constexpr int NQ = S / 2;         // shift pairs per row  -> x4 loads, k16 MMAs
+    constexpr bool ODD = (S & 1) != 0;  // last shift alone     -> x2 load,  k8 MMA
+    constexpr int NLD = NQ + (ODD ? 1 : 0);
 
-    // ldmatrix row addresses of this lane inside a slot, one per instruction.
-    constexpr int NMAT = 2 * S;          // matrices per tile per stage: 2 rows x S shifts
-    constexpr int NLD4 = NMAT / 4;       // x4 instructions
-    constexpr bool LD2 = (NMAT % 4) != 0;  // plus one x2
-    constexpr int NLD = NLD4 + (LD2 ? 1 : 0);
+    // per-lane byte offset inside a row of a slot for each load instruction
     u32 ld_off[NLD];
 #pragma unroll
     for (int q = 0; q < NLD; ++q) {
-      int f = 4 * q + (lane >> 3);
-      if (LD2 && q == NLD4) f = 4 * q + ((lane >> 3) & 1);
-      const u32 rowsel = (u32)(f / S), s = (u32)(f % S);
-      ld_off[q] = (rowsel * (u32)g.bw + s + l7) * 128u + (((u32)grp ^ ((s + l7) & 7u)) << 4);
+      const u32 mi = (u32)lane >> 3;                                      // matrix this lane addresses
+      const u32 sh = (ODD && q == NQ) ? (u32)(S - 1) : (u32)(2 * q) + (mi >> 1);  // column shift
+      const u32 px = 8u * (mi & 1u) + sh + l7;                            // pixel within the block
+      ld_off[q] = px * 128u + (((u32)grp ^ ((sh + l7) & 7u)) << 4);
     }
-    const u32 st_off = ((u32)((lane >> 3) & 1) * (u32)g.wt + l7) * 128u + (((u32)grp ^ l7) << 4);
+    const u32 st_off = (8u * (((u32)lane >> 3) & 1u) + l7) * 128u + (((u32)grp ^ l7) << 4);
+    const u32 in_row_bytes = g.in_pair_bytes >> 1;        // bw * 128
+    const u32 out_row_bytes = g.img_out_bytes >> 1;       // wt * 128
 
-    u32 in_off[TPW], out_off[TPW];
+    // Block tile t of this warp: image img of the slot, first pixel px0 of the block.
+    u32 tile_code[TPW];  // (img << 16) | (px0 * 128)
     bool tile_on[TPW];
 #pragma unroll
     for (int t = 0; t < TPW; ++t) {
       const int tidx = wsub + WPG * t;
       tile_on[t] = tidx < g.ntiles;
-      const int img = tidx / g.ncb, cb = tidx % g.ncb;
-      in_off[t] = (u32)(img * 2 * g.bw + cb * 8) * 128u;
-      out_off[t] = (u32)(img * 2 * g.wt + cb * 8) * 128u;
+      const int blk = tidx % g.nblk;
+      int px0 = 16 * blk;
+      if (px0 > g.wt - 16) px0 = g.wt - 16;  // the last block is shifted left, never past the tile
+      tile_code[t] = ((u32)(tidx / g.nblk) << 16) | ((u32)px0 * 128u);
     }
+    auto in_off = [&](int t) { return (tile_code[t] & 0xffffu) + (tile_code[t] >> 16) * g.img_in_bytes; };
+    auto out_off = [&](int t) { return (tile_code[t] & 0xffffu) + (tile_code[t] >> 16) * g.img_out_bytes; };
 
-    u32 wreg[NT];            // B fragments, one per tap
+    u32 wreg[NT];  // B fragments, one per tap
     float bias0 = 0.f, bias1 = 0.f;
     bool grp_on = false;
     int cur_ck = -1;
-    u32 X[TPW][WIN][S];      // register window: [tile][physical row][column shift]
+    // register window: [tile][physical row][shift pair][4] and, for odd S, [tile][row][2]
+    u32 XQ[TPW][WIN][NQ > 0 ? NQ : 1][4];
+    u32 XP[TPW][WIN][2];
 
-    Gw8Walk walk(u0, u1, g);
-    Gw8Segment seg;
     int slot = 0, ob = 0;
     u32 par = 0, opar = 0;
-    bool ok = true;
+    bool full_seen = mbar_test_wait(full(0), 0u);  // poll issued ahead of its use
 
-    while (ok && walk.next(seg)) {
-      if (seg.ck != cur_ck) {
-        cur_ck = seg.ck;
-        const int ch0 = seg.ck * 64 + grp * 8;  // first channel of this warp's group
+    // One stage.  PH0 fixes which physical window rows the PPS sub-steps overwrite.
+    auto stage = [&](auto ph0c, const int mask) -> bool {
+      constexpr int PH0 = decltype(ph0c)::value;
+      const u32 sbase = ring + (u32)slot * g.slot_bytes;
+      bool obuf_seen = mask ? mbar_test_wait(oempty(ob), opar ^ 1u) : true;
+      const u32 obase = obufs + (u32)ob * g.obuf_bytes;
+#pragma unroll
+      for (int u = 0; u < PPS; ++u) {
+        const int PH = (PH0 + u) % NPH;
+        if (grp_on) {
+#pragma unroll
+          for (int t = 0; t < TPW; ++t) {
+            if (tile_on[t]) {
+              const u32 a = opaque_add(sbase, in_off(t)) + (u32)u * g.in_pair_bytes;
+#pragma unroll
+              for (int row = 0; row < 2; ++row) {
+#pragma unroll
+                for (int q = 0; q < NQ; ++q)
+                  ldmatrix_x4<false>(XQ[t][2 * PH + row][q][0], XQ[t][2 * PH + row][q][1],
+                                     XQ[t][2 * PH + row][q][2], XQ[t][2 * PH + row][q][3],
+                                     a + (u32)row * in_row_bytes + ld_off[q]);
+                if (ODD)
+                  ldmatrix_x2<false>(XP[t][2 * PH + row][0], XP[t][2 * PH + row][1],
+                                     a + (u32)row * in_row_bytes + ld_off[NLD - 1]);
+              }
+            }
+          }
+        }
+        if (u == PPS - 1) {
+          // every row of the slot is in registers: hand it back and look ahead
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty(slot));
+          if (++slot == ns) {
+            slot = 0;
+            par ^= 1u;
+          }
+          full_seen = mbar_test_wait(full(slot), par);
+        }
+        if (mask & (1 << u)) {  // this sub-step completes an output pair
+          if (!obuf_seen) {
+            if (!mbar_wait(oempty(ob), opar ^ 1u, abortp)) return false;
+            obuf_seen = true;
+          }
+          if (grp_on) {
+#pragma unroll
+            for (int t = 0; t < TPW; ++t) {
+              if (tile_on[t]) {
+                const u32 o = opaque_add(obase, out_off(t)) + (u32)u * g.out_pair_bytes + st_off;
+#pragma unroll
+                for (int y = 0; y < 2; ++y) {  // the two output rows of the pair
+                  float acc[4] = {bias0, bias1, bias0, bias1};
+#pragma unroll
+                  for (int r = 0; r < Cfg::R; ++r) {
+                    // logical window row l = y + r (padded input row 2m + l) sits in
+                    // physical row 2*((PH + 1 + l/2) % NPH) + (l & 1)
+                    const int l = y + r;
+                    const int pr = 2 * ((PH + 1 + l / 2) % NPH) + (l & 1);
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q)
+                      mma_m16n8k16(acc, XQ[t][pr][q][0], XQ[t][pr][q][1], XQ[t][pr][q][2],
+                                   XQ[t][pr][q][3], wreg[r * S + 2 * q], wreg[r * S + 2 * q + 1]);
+                    if (ODD) mma_m16n8k8(acc, XP[t][pr][0], XP[t][pr][1], wreg[r * S + S - 1]);
+                  }
+                  const __half2 lo = __floats2half2_rn(acc[0], acc[1]);  // pixels 0-7 of the block
+                  const __half2 hi = __floats2half2_rn(acc[2], acc[3]);  // pixels 8-15
+                  stmatrix_x2(o + (u32)y * out_row_bytes, *reinterpret_cast<const u32*>(&lo),
+                              *reinterpret_cast<const u32*>(&hi));
+                }
+              }
+            }
+          }
+        }
+      }
+      if (mask) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ofull(ob));
+        if (++ob == nob) {
+          ob = 0;
+          opar ^= 1u;
+        }
+      }
+      return true;
+    };
+
+    for (;;) {
+      if (!full_seen && !mbar_wait(full(slot), par, abortp)) break;
+      const int4 d = *reinterpret_cast<const int4*>(&desc[slot]);  // ck, mask, ph0, flags
+      if (d.w & GW8_STAGE_END) break;
+      if (d.x != cur_ck) {
+        cur_ck = d.x;
+        const int gq = lane >> 2;  // fragment row / column index "g"
+        const int t4 = lane & 3;   // fragment pair index "t"
+        const int ch0 = d.x * 64 + grp * 8;  // first channel of this warp's group
         grp_on = ch0 < g.c;
         bias0 = bias1 = 0.f;
 #pragma unroll
@@ -215,98 +348,14 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
           }
         }
       }
-      const int nst = seg.m1 - seg.m0 + E;
-
-      // One stage: take slot j of the segment into the window, then (from stage E on)
-      // produce pair j - E.  PH = j mod NPH fixes which physical window rows are which.
-      auto stage = [&](auto phc, int j) -> bool {
-        constexpr int PH = decltype(phc)::value;
-        if (!mbar_wait(full(slot), par, abortp)) return false;
-        const u32 sbase = ring + (u32)slot * slot_bytes;
-        if (grp_on) {
-#pragma unroll
-          for (int t = 0; t < TPW; ++t) {
-            if (tile_on[t]) {
-              const u32 a = sbase + in_off[t];
-#pragma unroll
-              for (int q = 0; q < NLD4; ++q) {
-                const int f0 = 4 * q;
-                ldmatrix_x4<false>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
-                                   X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
-                                   X[t][2 * PH + (f0 + 2) / S][(f0 + 2) % S],
-                                   X[t][2 * PH + (f0 + 3) / S][(f0 + 3) % S], a + ld_off[q]);
-              }
-              if (LD2) {
-                const int f0 = 4 * NLD4;
-                ldmatrix_x2<false>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
-                                   X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
-                                   a + ld_off[NLD - 1]);
-              }
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty(slot));
-        if (++slot == ns) {
-          slot = 0;
-          par ^= 1u;
-        }
-        if (j >= E) {
-          if (!mbar_wait(oempty(ob), opar ^ 1u, abortp)) return false;
-          const u32 obase = obufs + (u32)ob * obuf_bytes;
-          if (grp_on) {
-#pragma unroll
-            for (int t = 0; t < TPW; ++t) {
-              if (tile_on[t]) {
-                float acc0[4] = {bias0, bias1, bias0, bias1};
-                float acc1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int i = 0; i < NT / 2; ++i) {
-                  // logical window row l (padded input row 2m + l) sits in physical row
-                  // 2*((PH + 1 + l/2) % NPH) + (l & 1)
-                  const int fa = 2 * i, fb = 2 * i + 1;
-                  const int ra = fa / S, sa = fa % S, rb = fb / S, sb = fb % S;
-                  const int pa0 = 2 * ((PH + 1 + ra / 2) % NPH) + (ra & 1);
-                  const int pa1 = 2 * ((PH + 1 + (ra + 1) / 2) % NPH) + ((ra + 1) & 1);
-                  const int pb0 = 2 * ((PH + 1 + rb / 2) % NPH) + (rb & 1);
-                  const int pb1 = 2 * ((PH + 1 + (rb + 1) / 2) % NPH) + ((rb + 1) & 1);
-                  if (i & 1)
-                    mma_m16n8k16(acc1, X[t][pa0][sa], X[t][pa1][sa], X[t][pb0][sb], X[t][pb1][sb],
-                                 wreg[fa], wreg[fb]);
-                  else
-                    mma_m16n8k16(acc0, X[t][pa0][sa], X[t][pa1][sa], X[t][pb0][sb], X[t][pb1][sb],
-                                 wreg[fa], wreg[fb]);
-                }
-                if (NT & 1) {
-                  const int fa = NT - 1;
-                  const int ra = fa / S, sa = fa % S;
-                  const int pa0 = 2 * ((PH + 1 + ra / 2) % NPH) + (ra & 1);
-                  const int pa1 = 2 * ((PH + 1 + (ra + 1) / 2) % NPH) + ((ra + 1) & 1);
-                  mma_m16n8k8(acc1, X[t][pa0][sa], X[t][pa1][sa], wreg[fa]);
-                }
-                const __half2 top = __floats2half2_rn(acc0[0] + acc1[0], acc0[1] + acc1[1]);
-                const __half2 bot = __floats2half2_rn(acc0[2] + acc1[2], acc0[3] + acc1[3]);
-                stmatrix_x2(obase + out_off[t] + st_off, *reinterpret_cast<const u32*>(&top),
-                            *reinterpret_cast<const u32*>(&bot));
-              }
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(ofull(ob));
-          if (++ob == nob) {
-            ob = 0;
-            opar ^= 1u;
-          }
-        }
-        return true;
-      };
-
-      for (int j = 0; ok && j < nst; j += NPH) {
-        ok = stage(IntC<0>{}, j);
-        if (NPH > 1 && ok && j + 1 < nst) ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, j + 1);
-        if (NPH > 2 && ok && j + 2 < nst) ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, j + 2);
-      }
+      bool ok;
+      if (d.z == 0)
+        ok = stage(IntC<0>{}, d.y);
+      else if (d.z == 1)
+        ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, d.y);
+      else
+        ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, d.y);
+      if (!ok) break;
     }
   }
 

@@ -26,11 +26,11 @@ namespace spio_b200 {
 // Scratch layout: [chunk][part][64 local out-channels][taps][8 in-channels] fp32 with
 // part = split * WPG + warp_sub, n_parts = n_split * WPG.
 template <class Cfg>
-__global__ void __launch_bounds__((Cfg::NCW + 1) * 32, 1)
+__global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
 conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
                         const __grid_constant__ TensorMap dy_map, const Gw8Geom g,
                         float* __restrict__ scratch, int ns, int* __restrict__ status) {
-  constexpr int S = Cfg::S, WPG = Cfg::WPG, TPW = Cfg::TPW;
+  constexpr int S = Cfg::S, WPG = Cfg::WPG, TPW = Cfg::TPW, PPS = Cfg::PPS;
   constexpr int E = Cfg::E, WIN = Cfg::WIN, NT = Cfg::NT, NCW = Cfg::NCW;
   constexpr int NPH = WIN / 2;
   constexpr int NACC = (NT + 1) / 2;
@@ -41,8 +41,10 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
   __shared__ int abort_flag;
 
   const u32 base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const u32 xslot_bytes = (u32)(g.nb * 2 * g.bw) * 128u;
-  const u32 dslot_bytes = (u32)(g.nb * 2 * g.wt) * 128u;
+  const u32 x_pair_bytes = (u32)(2 * g.bw) * 128u;   // one row pair of one image of x
+  const u32 d_pair_bytes = (u32)(2 * g.wt) * 128u;   // one row pair of one image of dy
+  const u32 xslot_bytes = (u32)(g.nb * PPS) * x_pair_bytes;  // [nb][2*PPS rows][bw][64]
+  const u32 dslot_bytes = (u32)(g.nb * PPS) * d_pair_bytes;  // [nb][2*PPS rows][wt][64]
   const u32 stage_bytes = xslot_bytes + dslot_bytes;
   const u32 bar0 = smem_u32(bars);
   auto full = [&](int i) { return bar0 + 8u * (u32)i; };
@@ -69,6 +71,12 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
   const int lane = threadIdx.x & 31;
   volatile int* abortp = &abort_flag;
 
+  // Stage i of a segment brings the x row pairs PPS*i .. PPS*i+PPS-1 and the dy row pairs
+  // PPS*i-E .. PPS*i+PPS-1-E (relative to the segment); pair q = PPS*i+u-E is accumulated
+  // in sub-step u if it lies in [0, L).
+  auto stages_of = [&](const Gw8Segment& sg) { return (sg.m1 - sg.m0 + E + PPS - 1) / PPS; };
+  auto stage_has_pairs = [&](int i) { return PPS * i + PPS - 1 >= E; };
+
   if (warp == NCW) {
     // ------------------------------------------------------------ load warp
     if (lane == 0) {
@@ -81,21 +89,22 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
         Gw8Walk walk(ck * per_chunk + s0, ck * per_chunk + s1, g);
         Gw8Segment seg;
         while (ok && walk.next(seg)) {
-          const int nst = seg.m1 - seg.m0 + E;
+          const int nst = stages_of(seg);
           const int c0 = seg.ck * 64;
           const int n0 = seg.ig * g.nb;
-          for (int j = 0; j < nst; ++j) {
+          for (int i = 0; i < nst; ++i) {
             if (!mbar_wait(empty(slot), par ^ 1u, abortp)) {
               ok = false;
               break;
             }
             const u32 dst = base + (u32)slot * stage_bytes;
-            mbar_arrive_expect_tx(full(slot), j >= E ? stage_bytes : xslot_bytes);
+            const bool with_dy = stage_has_pairs(i);
+            mbar_arrive_expect_tx(full(slot), with_dy ? stage_bytes : xslot_bytes);
             tma_load_4d(dst, &x_map, full(slot), c0, seg.ct * g.wt - g.pad_w,
-                        2 * (seg.m0 + j) - g.pad_h, n0);
-            if (j >= E)
+                        2 * (seg.m0 + PPS * i) - g.pad_h, n0);
+            if (with_dy)
               tma_load_4d(dst + xslot_bytes, &dy_map, full(slot), c0, seg.ct * g.wt,
-                          2 * (seg.m0 + j - E), n0);
+                          2 * (seg.m0 + PPS * i - E), n0);
             if (++slot == ns) {
               slot = 0;
               par ^= 1u;
@@ -134,8 +143,8 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
       const int tidx = wsub + WPG * t;
       tile_on[t] = tidx < g.ntiles;
       const int img = tidx / g.ncb, cb = tidx % g.ncb;
-      x_off[t] = (u32)(img * 2 * g.bw + cb * 8) * 128u;
-      d_off[t] = (u32)(img * 2 * g.wt + cb * 8) * 128u;
+      x_off[t] = (u32)(img * 2 * PPS * g.bw + cb * 8) * 128u;
+      d_off[t] = (u32)(img * 2 * PPS * g.wt + cb * 8) * 128u;
     }
 
     u32 X[TPW][WIN][S];
@@ -143,6 +152,7 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
     int slot = 0;
     u32 par = 0;
     bool ok = true;
+    bool full_seen = mbar_test_wait(full(0), 0u);
     const int n_parts = g.n_split * WPG;
 
     for (int ck = cl; ok && ck < g.n_chunks; ck += chunk_step) {
@@ -155,49 +165,56 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
       Gw8Walk walk(ck * per_chunk + s0, ck * per_chunk + s1, g);
       Gw8Segment seg;
       while (ok && walk.next(seg)) {
-        const int nst = seg.m1 - seg.m0 + E;
+        const int nst = stages_of(seg);
+        const int len = seg.m1 - seg.m0;
 
-        auto stage = [&](auto phc, int j) -> bool {
-          constexpr int PH = decltype(phc)::value;
-          if (!mbar_wait(full(slot), par, abortp)) return false;
+        auto stage = [&](auto ph0c, int i) -> bool {
+          constexpr int PH0 = decltype(ph0c)::value;
+          if (!full_seen && !mbar_wait(full(slot), par, abortp)) return false;
           const u32 xbase = base + (u32)slot * stage_bytes;
           const u32 dbase = xbase + xslot_bytes;
           if (grp_on) {
 #pragma unroll
-            for (int t = 0; t < TPW; ++t) {
-              if (tile_on[t]) {
-                const u32 a = xbase + x_off[t];
+            for (int u = 0; u < PPS; ++u) {
+              const int PH = (PH0 + u) % NPH;
+              const int q = PPS * i + u - E;
+              const bool pair_on = q >= 0 && q < len;
 #pragma unroll
-                for (int q = 0; q < NLD4; ++q) {
-                  const int f0 = 4 * q;
-                  ldmatrix_x4<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
-                                    X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
-                                    X[t][2 * PH + (f0 + 2) / S][(f0 + 2) % S],
-                                    X[t][2 * PH + (f0 + 3) / S][(f0 + 3) % S], a + ld_off[q]);
-                }
-                if (LD2) {
-                  const int f0 = 4 * NLD4;
-                  ldmatrix_x2<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
-                                    X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
-                                    a + ld_off[NLD - 1]);
-                }
-                if (j >= E) {
-                  u32 d0, d1;
-                  ldmatrix_x2<true>(d0, d1, dbase + d_off[t] + dy_off);
+              for (int t = 0; t < TPW; ++t) {
+                if (tile_on[t]) {
+                  const u32 a = opaque_add(xbase, x_off[t]) + (u32)u * x_pair_bytes;
 #pragma unroll
-                  for (int i = 0; i < NACC; ++i) {
-                    const int fa = 2 * i, fb = 2 * i + 1;
-                    const int ra = fa / S, sa = fa % S;
-                    const int pa0 = 2 * ((PH + 1 + ra / 2) % NPH) + (ra & 1);
-                    const int pa1 = 2 * ((PH + 1 + (ra + 1) / 2) % NPH) + ((ra + 1) & 1);
-                    if (fb < NT) {
-                      const int rb = fb / S, sb = fb % S;
-                      const int pb0 = 2 * ((PH + 1 + rb / 2) % NPH) + (rb & 1);
-                      const int pb1 = 2 * ((PH + 1 + (rb + 1) / 2) % NPH) + ((rb + 1) & 1);
-                      mma_m16n8k16(acc[i], X[t][pa0][sa], X[t][pb0][sb], X[t][pa1][sa],
-                                   X[t][pb1][sb], d0, d1);
-                    } else {
-                      mma_m16n8k16(acc[i], X[t][pa0][sa], 0u, X[t][pa1][sa], 0u, d0, d1);
+                  for (int v = 0; v < NLD4; ++v) {
+                    const int f0 = 4 * v;
+                    ldmatrix_x4<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
+                                      X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
+                                      X[t][2 * PH + (f0 + 2) / S][(f0 + 2) % S],
+                                      X[t][2 * PH + (f0 + 3) / S][(f0 + 3) % S], a + ld_off[v]);
+                  }
+                  if (LD2) {
+                    const int f0 = 4 * NLD4;
+                    ldmatrix_x2<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
+                                      X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
+                                      a + ld_off[NLD - 1]);
+                  }
+                  if (pair_on) {
+                    u32 d0, d1;
+                    ldmatrix_x2<true>(d0, d1, opaque_add(dbase, d_off[t]) + (u32)u * d_pair_bytes + dy_off);
+#pragma unroll
+                    for (int k = 0; k < NACC; ++k) {
+                      const int fa = 2 * k, fb = 2 * k + 1;
+                      const int ra = fa / S, sa = fa % S;
+                      const int pa0 = 2 * ((PH + 1 + ra / 2) % NPH) + (ra & 1);
+                      const int pa1 = 2 * ((PH + 1 + (ra + 1) / 2) % NPH) + ((ra + 1) & 1);
+                      if (fb < NT) {
+                        const int rb = fb / S, sb = fb % S;
+                        const int pb0 = 2 * ((PH + 1 + rb / 2) % NPH) + (rb & 1);
+                        const int pb1 = 2 * ((PH + 1 + (rb + 1) / 2) % NPH) + ((rb + 1) & 1);
+                        mma_m16n8k16(acc[k], X[t][pa0][sa], X[t][pb0][sb], X[t][pa1][sa],
+                                     X[t][pb1][sb], d0, d1);
+                      } else {
+                        mma_m16n8k16(acc[k], X[t][pa0][sa], 0u, X[t][pa1][sa], 0u, d0, d1);
+                      }
                     }
                   }
                 }
@@ -210,13 +227,18 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
             slot = 0;
             par ^= 1u;
           }
+          full_seen = mbar_test_wait(full(slot), par);
           return true;
         };
 
-        for (int j = 0; ok && j < nst; j += NPH) {
-          ok = stage(IntC<0>{}, j);
-          if (NPH > 1 && ok && j + 1 < nst) ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, j + 1);
-          if (NPH > 2 && ok && j + 2 < nst) ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, j + 2);
+        for (int i = 0; ok && i < nst; ++i) {
+          const int ph0 = (PPS * i) % NPH;
+          if (ph0 == 0)
+            ok = stage(IntC<0>{}, i);
+          else if (ph0 == 1)
+            ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, i);
+          else
+            ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, i);
         }
       }
 

@@ -44,7 +44,7 @@ int fail_cuda(const char* what, cudaError_t e) {
 __device__ int g_status_word;
 
 constexpr int kMaxDevices = 64;
-constexpr int kFwdStaticSmem = 512;    // >= static shared memory of the kernels
+constexpr int kFwdStaticSmem = 1024;   // >= static shared memory of the kernels
 constexpr int kAlignSlack = 1024;      // dynamic shared memory is re-aligned to 1 KiB
 
 struct DeviceInfo {
@@ -152,20 +152,27 @@ int check_shape(const spio_gw8_shape* sh) {
 int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
               const std::vector<Gw8Variant>& variants, Plan* plan) {
   if (check_shape(sh)) return 1;
-  static const spio_gw8_tune kAuto = {0, 0, 0, 0, 0, 0, 0};
+  static const spio_gw8_tune kAuto = {0, 0, 0, 0, 0, 0, 0, 0};
   const spio_gw8_tune& t = tune ? *tune : kAuto;
   const int p = sh->h + 2 * sh->pad_h - sh->r + 1;
   const int q = sh->w + 2 * sh->pad_w - sh->s + 1;
 
+  // Unless the caller asks otherwise, the forward kernel streams one row pair per slot
+  // (its register window then fits without spills) and the weight-gradient kernel two.
+  const int default_pps = kind == SPIO_GW8_WGRAD ? 2 : 1;
   const Gw8Variant* v = nullptr;
-  for (const Gw8Variant& cand : variants) {
-    if (cand.r != sh->r || cand.s != sh->s) continue;
-    if (t.wpg && cand.wpg != t.wpg) continue;
-    if (t.tpw && cand.tpw != t.tpw) continue;
-    v = &cand;
-    break;
+  for (int pass = 0; pass < 2 && v == nullptr; ++pass) {
+    for (const Gw8Variant& cand : variants) {
+      if (cand.r != sh->r || cand.s != sh->s) continue;
+      if (t.wpg && cand.wpg != t.wpg) continue;
+      if (t.tpw && cand.tpw != t.tpw) continue;
+      if (t.pps && cand.pps != t.pps) continue;
+      if (pass == 0 && !t.pps && cand.pps != default_pps) continue;
+      v = &cand;
+      break;
+    }
   }
-  if (v == nullptr) return fail("no compiled kernel variant matches r, s, wpg, tpw");
+  if (v == nullptr) return fail("no compiled kernel variant matches r, s, wpg, tpw, pps");
 
   Plan pl;
   pl.kind = kind;
@@ -181,51 +188,59 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
     g.in_h = sh->h, g.in_w = sh->w, g.out_h = p, g.out_w = q;
     g.pad_h = sh->pad_h, g.pad_w = sh->pad_w;
   }
-  const int max_tiles = v->wpg * v->tpw;
-  const int e = sh->r / 2;
+  // Tile capacity of the compute warps.  The weight-gradient kernel works on tiles of 8
+  // pixels x 2 rows (TPW per warp); the forward kernel on blocks of 16 pixels x 1 row, of
+  // which a warp keeps (TPW + 1) / 2, so both hold the same number of window registers.
+  const bool fwd = kind != SPIO_GW8_WGRAD;
+  const int max_tiles = fwd ? v->wpg * ((v->tpw + 1) / 2) : v->wpg * v->tpw;
+  const int min_ncb = fwd ? 2 : 1;  // a forward column tile is at least one 16-pixel block
+  auto tiles_needed = [&](int ncb8) { return fwd ? cdiv(ncb8 < 2 ? 2 : ncb8, 2) : ncb8; };
+  const int pps = v->pps;
   const int avail = smem_optin - kFwdStaticSmem - kAlignSlack;
   const int qb = cdiv(g.out_w, 8);
 
   int ncb = t.ncb ? t.ncb : 0;
   if (ncb <= 0) {
-    const int n_ct0 = cdiv(qb, max_tiles);
+    const int n_ct0 = cdiv(tiles_needed(qb), max_tiles);
     ncb = cdiv(qb, n_ct0);
   }
-  if (ncb > max_tiles) return fail("ncb exceeds wpg * tpw");
+  if (ncb < min_ncb) ncb = min_ncb;
+  if (tiles_needed(ncb) > max_tiles) return fail("ncb exceeds the tile capacity of wpg * tpw");
   int nb = t.nb ? t.nb : 0;
   if (nb <= 0) {
     nb = 1;
     if (ncb >= qb) {  // the whole width fits one column tile: batch images into a slot
-      nb = max_tiles / ncb;
+      nb = max_tiles / tiles_needed(ncb);
       if (nb > sh->n) nb = sh->n;
       if (nb < 1) nb = 1;
     }
   }
-  if (nb * ncb > max_tiles) return fail("nb * ncb exceeds wpg * tpw");
+  if (nb * tiles_needed(ncb) > max_tiles) return fail("nb * ncb exceeds the tile capacity of wpg * tpw");
 
-  const int min_slots = e + 2;
+  const int min_slots = 2;
   for (;;) {
     g.ncb = ncb;
     g.nb = nb;
     g.wt = 8 * ncb;
     g.bw = round_up(g.wt + sh->s - 1, 8);
-    const int slot = nb * 2 * g.bw * 128;
-    const int oslot = nb * 2 * g.wt * 128;
+    const int slot = nb * 2 * pps * g.bw * 128;   // one ring slot of the streamed operand
+    const int oslot = nb * 2 * pps * g.wt * 128;  // staging buffer (fwd) / dy part of a slot (wgrad)
     int ns, nob = 0;
     if (kind == SPIO_GW8_WGRAD) {
       ns = avail / (slot + oslot);
     } else {
-      nob = t.nob ? t.nob : 2;
+      nob = t.nob ? t.nob : 2;  // measured: more staging buffers do not help the forward kernel
       if (nob > 4) return fail("nob must be at most 4");
       ns = (avail - nob * oslot) / slot;
     }
     if (ns > 16) ns = 16;
+    if (!t.ns && ns > 8) ns = 8;  // a deeper ring buys nothing and shrinks the L1 cache
     if (t.ns) {
       if (t.ns > ns) return fail("requested ring does not fit in shared memory");
       ns = t.ns;
     }
     const bool box_ok = g.bw <= 256 && nb <= 256;
-    if (ns >= min_slots && box_ok && (t.nb || t.ncb || slot <= 32 * 1024 || (nb == 1 && ncb == 1))) {
+    if (ns >= min_slots && box_ok && (t.nb || t.ncb || slot <= 48 * 1024 || (nb == 1 && ncb == min_ncb))) {
       pl.ns = ns;
       pl.nob = nob;
       pl.smem = kAlignSlack + ns * (kind == SPIO_GW8_WGRAD ? slot + oslot : slot) + nob * oslot;
@@ -234,12 +249,19 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
     if (t.nb || t.ncb) return fail("requested tile does not fit in shared memory");
     if (nb > 1)
       nb = nb / 2;
-    else if (ncb > 1)
-      ncb = cdiv(ncb, 2);
+    else if (ncb > min_ncb)
+      ncb = cdiv(ncb, 2) < min_ncb ? min_ncb : cdiv(ncb, 2);
     else
       return fail("tile does not fit in shared memory");
   }
-  g.ntiles = g.nb * g.ncb;
+  g.nblk = cdiv(g.wt, 16);
+  g.ntiles = g.nb * tiles_needed(g.ncb);
+  g.in_pair_bytes = (unsigned)(2 * g.bw * 128);
+  g.out_pair_bytes = (unsigned)(g.nb * 2 * g.wt * 128);
+  g.slot_bytes = (unsigned)(g.nb * pps) * g.in_pair_bytes;
+  g.obuf_bytes = (unsigned)pps * g.out_pair_bytes;
+  g.img_in_bytes = (unsigned)(2 * pps * g.bw * 128);
+  g.img_out_bytes = (unsigned)(2 * g.wt * 128);
   g.n_chunks = cdiv(g.c, 64);
   g.n_ig = cdiv(g.n, g.nb);
   g.n_ct = cdiv(qb, g.ncb);
@@ -268,11 +290,12 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
   return 0;
 }
 
-int encode_map(CUtensorMap* m, const void* ptr, int c, int w, int h, int n, int box_w, int box_n) {
+int encode_map(CUtensorMap* m, const void* ptr, int c, int w, int h, int n, int box_w, int box_h,
+               int box_n) {
   if ((reinterpret_cast<size_t>(ptr) & 15u) != 0) return fail("tensor pointers must be 16-byte aligned");
   const cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
   const cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};
-  const cuuint32_t box[4] = {64u, (cuuint32_t)box_w, 2u, (cuuint32_t)box_n};
+  const cuuint32_t box[4] = {64u, (cuuint32_t)box_w, (cuuint32_t)box_h, (cuuint32_t)box_n};
   const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(ptr), dims,
                               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -281,8 +304,8 @@ int encode_map(CUtensorMap* m, const void* ptr, int c, int w, int h, int n, int 
   if (r != CUDA_SUCCESS) {
     char buf[160];
     snprintf(buf, sizeof buf,
-             "CUDA error: cuTensorMapEncodeTiled failed with code %d (dims %d,%d,%d,%d box 64,%d,2,%d)",
-             (int)r, c, w, h, n, box_w, box_n);
+             "CUDA error: cuTensorMapEncodeTiled failed with code %d (dims %d,%d,%d,%d box 64,%d,%d,%d)",
+             (int)r, c, w, h, n, box_w, box_h, box_n);
     return fail(buf);
   }
   return 0;
@@ -299,8 +322,8 @@ int launch_fwd(int kind, void* out, const void* in, const void* w, const float* 
   if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
   const Gw8Geom& g = pl.g;
   CUtensorMap in_map, out_map;
-  if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, g.bw, g.nb)) return 1;
-  if (encode_map(&out_map, out, g.c, g.out_w, g.out_h, g.n, g.wt, g.nb)) return 1;
+  if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
+  if (encode_map(&out_map, out, g.c, g.out_w, g.out_h, g.n, g.wt, 2, g.nb)) return 1;
   if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
   const __half* wp = static_cast<const __half*>(w);
   int ns = pl.ns, nob = pl.nob;
@@ -323,8 +346,8 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
     return fail("dw and scratch must be 16-byte aligned");
   const Gw8Geom& g = pl.g;
   CUtensorMap x_map, dy_map;
-  if (encode_map(&x_map, x, g.c, g.in_w, g.in_h, g.n, g.bw, g.nb)) return 1;
-  if (encode_map(&dy_map, dy, g.c, g.out_w, g.out_h, g.n, g.wt, g.nb)) return 1;
+  if (encode_map(&x_map, x, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
+  if (encode_map(&dy_map, dy, g.c, g.out_w, g.out_h, g.n, g.wt, 2 * pl.v->pps, g.nb)) return 1;
   float* sc = static_cast<float*>(scratch);
   int ns = pl.ns;
   int* status = d->status;
@@ -379,6 +402,7 @@ size_t weight_elems(const spio_gw8_shape* sh) { return (size_t)sh->c * sh->r * s
 void fill_info(const Plan& pl, spio_gw8_plan_info* info) {
   info->wpg = pl.v->wpg;
   info->tpw = pl.v->tpw;
+  info->pps = pl.v->pps;
   info->ns = pl.ns;
   info->nob = pl.nob;
   info->ncb = pl.g.ncb;
@@ -521,7 +545,7 @@ int spio_conv2d_gw8_num_variants(void) {
   return (int)g_variants.size();
 }
 
-int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw) {
+int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw, int* pps) {
   std::lock_guard<std::mutex> lock(g_mutex);
   load_variants_locked();
   if (i < 0 || i >= (int)g_variants.size()) return fail("variant index out of range");
@@ -529,6 +553,7 @@ int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw) {
   if (s) *s = g_variants[i].s;
   if (wpg) *wpg = g_variants[i].wpg;
   if (tpw) *tpw = g_variants[i].tpw;
+  if (pps) *pps = g_variants[i].pps;
   return 0;
 }
 

@@ -8,9 +8,9 @@
 //   pair       two consecutive output rows (2m, 2m+1).
 //   col tile   Wt = 8*ncb output columns, ncb "column blocks" of 8 pixels.
 //   image group NB consecutive images that share one box.
-//   slot       one TMA box of the streamed tensor: NB images x 2 rows x BW columns
+//   slot       one TMA box of the streamed tensor: NB images x 2*PPS rows x BW columns
 //              x 64 channels, BW = round_up(Wt + S - 1, 8).  Slot j of a segment
-//              holds padded rows 2j and 2j+1 (padded row = input row + pad_h).
+//              holds padded rows 2*PPS*j .. 2*PPS*(j+1)-1 (padded row = input row + pad_h).
 //   segment    a run of pairs of one (chunk, image group, col tile) that one CTA
 //              streams top to bottom, carrying its register window of input rows.
 //
@@ -47,23 +47,49 @@ struct Gw8Geom {
   int nb;              // images per slot
   int wt;              // 8 * ncb
   int bw;              // slot width in pixels, multiple of 8
-  int ntiles;          // nb * ncb  (<= WPG * TPW)
+  int nblk;            // fprop/dgrad: 16-pixel blocks per column tile, ceil(wt / 16)
+  int ntiles;          // tiles per slot: nb * nblk (fprop/dgrad) or nb * ncb (wgrad); <= WPG * TPW
   int dgrad;           // 1: weights are used transposed and flipped
   int n_split;         // wgrad: CTAs that share one chunk
+  // byte sizes derived from the above (kept here so that the kernels read them from the
+  // constant bank instead of holding them in registers); pps = row pairs per slot
+  unsigned in_pair_bytes;    // 2 rows of one image of the streamed operand: 2*bw*128
+  unsigned out_pair_bytes;   // 2 rows of nb images of the tiled operand:   nb*2*wt*128
+  unsigned slot_bytes;       // nb * pps * in_pair_bytes
+  unsigned obuf_bytes;       // pps * out_pair_bytes (fwd staging buffer / dy part of a wgrad slot)
+  unsigned img_in_bytes;     // one image inside a slot:        2*pps*bw*128
+  unsigned img_out_bytes;    // one image inside a staging pair: 2*wt*128
 };
 
+// What the load warp tells the compute warps about the slot it has just filled.
+struct alignas(16) Gw8StageDesc {
+  int ck;     // chunk the slot belongs to
+  int mask;   // bit u set: sub-step u completes an output pair
+  int ph0;    // window phase of sub-step 0: (PPS * stage index) mod (WIN / 2)
+  int flags;  // GW8_STAGE_END: no more work, the slot holds no data
+};
+enum { GW8_STAGE_END = 1 };
+
 // Compile-time tile configuration.
-//   R, S   filter size;  WPG warps per group;  TPW tiles (8 px x 2 rows) per warp.
+//   R, S   filter size;  WPG warps per group;  TPW tiles (8 px x 2 rows) per warp;
+//   PPS    row pairs per ring slot (one barrier hand-off per 2*PPS rows).
 // The number of ring slots and of output staging buffers is a launch argument.
-template <int R_, int S_, int WPG_, int TPW_>
+template <int R_, int S_, int WPG_, int TPW_, int PPS_ = 1>
 struct Gw8Config {
-  static constexpr int R = R_, S = S_, WPG = WPG_, TPW = TPW_;
+  static constexpr int R = R_, S = S_, WPG = WPG_, TPW = TPW_, PPS = PPS_;
   static constexpr int E = R / 2;          // extra slots a pair needs below its own
   static constexpr int WIN = 2 * E + 2;    // rows of the register window
   static constexpr int NT = R * S;         // taps
   static constexpr int NCW = 8 * WPG;      // consumer warps
   static constexpr int THREADS = (NCW + 2) * 32;  // + load warp + store warp
   static constexpr int MAX_TILES = WPG * TPW;
+  static constexpr int WGRAD_THREADS = (NCW + 1) * 32;  // no store warp
+};
+
+// Carries a compile-time integer into a generic lambda.
+template <int V>
+struct IntC {
+  static constexpr int value = V;
 };
 
 // One segment of a CTA's span.

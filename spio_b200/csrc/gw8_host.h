@@ -20,10 +20,11 @@ struct Gw8Tune {
   int ncb;  // column blocks per column tile
   int nb;   // images per slot
   int grid; // CTAs (0: one per SM)
+  int pps;  // row pairs per ring slot (compiled variants only)
 };
 
 struct Gw8Variant {
-  int r, s, wpg, tpw;
+  int r, s, wpg, tpw, pps;
   int fwd_threads, wgrad_threads;
   const void* fwd_kernel;    // conv2d_gw8_fwd_kernel<Cfg>
   const void* wgrad_kernel;  // conv2d_gw8_wgrad_kernel<Cfg>

@@ -30,6 +30,15 @@ __device__ __forceinline__ u64 globaltimer_ns() {
   return t;
 }
 
+// An addition the compiler can neither hoist out of a loop nor fold with its neighbours.
+// Used where precomputing every loop-invariant address would cost more registers than the
+// adds it saves.
+__device__ __forceinline__ u32 opaque_add(u32 a, u32 b) {
+  u32 r;
+  asm volatile("add.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(u32 bar, u32 count) {
@@ -54,6 +63,20 @@ __device__ __forceinline__ bool mbar_try_wait(u32 bar, u32 parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Non-blocking poll.  Issued ahead of the point where the answer is needed, its latency
+// (tens of cycles) overlaps the instructions in between.
+__device__ __forceinline__ bool mbar_test_wait(u32 bar, u32 parity) {
+  u32 ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)

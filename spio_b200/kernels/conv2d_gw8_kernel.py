@@ -6,8 +6,9 @@ kernel is persistent and streams row pairs through a shared-memory ring, so a
 configuration fixes the warp mapping and the ring instead:
 
     wpg  compute warps per channel group        tpw  8-pixel x 2-row tiles per warp
-    ncb  8-pixel column blocks per column tile   nb   images per ring slot
-    ns   ring slots                              nob  output staging buffers
+    pps  row pairs per ring slot                 ncb  8-pixel column blocks per column tile
+    nb   images per ring slot                    ns   ring slots
+    nob  output staging buffers
 
 A zero means "let the launch planner choose".
 """
@@ -30,6 +31,7 @@ from .kernel_factory import KernelFactory
 class Conv2dGw8Config:
     wpg: int = 0
     tpw: int = 0
+    pps: int = 0
     ncb: int = 0
     nb: int = 0
     ns: int = 0
@@ -40,15 +42,15 @@ class Conv2dGw8Config:
 
 
 def compiled_variants(r: int, s: int) -> List[tuple]:
-    """(wpg, tpw) pairs compiled into the library for an r x s filter."""
+    """(wpg, tpw, pps) triples compiled into the library for an r x s filter."""
     lib = _clib.load()
     out = []
-    vr, vs, vw, vt = (ctypes.c_int() for _ in range(4))
+    vr, vs, vw, vt, vp = (ctypes.c_int() for _ in range(5))
     for i in range(lib.spio_conv2d_gw8_num_variants()):
         lib.spio_conv2d_gw8_variant(i, ctypes.byref(vr), ctypes.byref(vs), ctypes.byref(vw),
-                                    ctypes.byref(vt))
+                                    ctypes.byref(vt), ctypes.byref(vp))
         if (vr.value, vs.value) == (r, s):
-            out.append((vw.value, vt.value))
+            out.append((vw.value, vt.value, vp.value))
     return out
 
 
@@ -63,21 +65,24 @@ def plan_is_valid(kind: int, params, tune: dict, device_attr) -> bool:
     return rc == 0
 
 
-def enumerate_tiles(params, out_w: int, wpg: int, tpw: int) -> Iterator[tuple]:
+def enumerate_tiles(params, out_w: int, wpg: int, tpw: int, forward: bool = False) -> Iterator[tuple]:
     """(ncb, nb) candidates: the width cut into 1..4 column tiles; several images per slot
-    only when one tile spans the whole width."""
-    max_tiles = wpg * tpw
+    only when one tile spans the whole width.  ncb counts 8-pixel column blocks.  The
+    weight-gradient kernel holds wpg * tpw tiles of 8 pixels; the forward kernel holds
+    wpg * ceil(tpw / 2) blocks of 16 pixels and its column tile is at least 16 pixels wide."""
+    max_tiles = wpg * ((tpw + 1) // 2) if forward else wpg * tpw
+    need = (lambda ncb: divup(max(ncb, 2), 2)) if forward else (lambda ncb: ncb)
     col_blocks = divup(out_w, 8)
     seen = set()
     for n_ct in range(1, 5):
-        ncb = divup(col_blocks, n_ct)
-        if ncb > max_tiles or ncb in seen:
+        ncb = max(divup(col_blocks, n_ct), 2 if forward else 1)
+        if need(ncb) > max_tiles or ncb in seen:
             continue
         seen.add(ncb)
         yield ncb, 1
         if ncb >= col_blocks:
             nb = 2
-            while nb * ncb <= max_tiles and nb <= params.n:
+            while nb * need(ncb) <= max_tiles and nb <= params.n:
                 yield ncb, nb
                 nb *= 2
 
@@ -85,11 +90,11 @@ def enumerate_tiles(params, out_w: int, wpg: int, tpw: int) -> Iterator[tuple]:
 def _get_configs(params: Conv2dGw8Params, device_attr, igrad: bool = False) -> Iterator[Conv2dGw8Config]:
     kind = _clib.DGRAD if igrad else _clib.FPROP
     out_w = params.w if igrad else params.q
-    for wpg, tpw in compiled_variants(params.r, params.s):
-        for ncb, nb in enumerate_tiles(params, out_w, wpg, tpw):
-            for ns in (0, 4, 6, 8):
+    for wpg, tpw, pps in compiled_variants(params.r, params.s):
+        for ncb, nb in enumerate_tiles(params, out_w, wpg, tpw, forward=True):
+            for ns in (0, 3, 4, 6):
                 for nob in (2, 3):
-                    cfg = Conv2dGw8Config(wpg=wpg, tpw=tpw, ncb=ncb, nb=nb, ns=ns, nob=nob)
+                    cfg = Conv2dGw8Config(wpg=wpg, tpw=tpw, pps=pps, ncb=ncb, nb=nb, ns=ns, nob=nob)
                     if plan_is_valid(kind, params, cfg.as_tune(), device_attr):
                         yield cfg
 

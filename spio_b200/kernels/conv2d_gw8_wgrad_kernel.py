@@ -21,6 +21,7 @@ from .kernel_factory import KernelFactory
 class Conv2dGw8WgradConfig:
     wpg: int = 0
     tpw: int = 0
+    pps: int = 0
     ncb: int = 0
     nb: int = 0
     ns: int = 0
@@ -30,10 +31,10 @@ class Conv2dGw8WgradConfig:
 
 
 def _get_configs(params: Conv2dGw8Params, device_attr) -> Iterator[Conv2dGw8WgradConfig]:
-    for wpg, tpw in compiled_variants(params.r, params.s):
+    for wpg, tpw, pps in compiled_variants(params.r, params.s):
         for ncb, nb in enumerate_tiles(params, params.q, wpg, tpw):
-            for ns in (0, 3, 4, 6):
-                cfg = Conv2dGw8WgradConfig(wpg=wpg, tpw=tpw, ncb=ncb, nb=nb, ns=ns)
+            for ns in (0, 2, 3, 4):
+                cfg = Conv2dGw8WgradConfig(wpg=wpg, tpw=tpw, pps=pps, ncb=ncb, nb=nb, ns=ns)
                 if plan_is_valid(_clib.WGRAD, params, cfg.as_tune(), device_attr):
                     yield cfg
 

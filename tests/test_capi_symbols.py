@@ -31,8 +31,8 @@ def test_header_symbols_are_exported_and_bound():
 
 def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(_clib.Shape) == 8 * 4
-    assert ctypes.sizeof(_clib.Tune) == 7 * 4
-    assert ctypes.sizeof(_clib.PlanInfo) == 14 * 4 + 8
+    assert ctypes.sizeof(_clib.Tune) == 8 * 4
+    assert ctypes.sizeof(_clib.PlanInfo) == 16 * 4 + 8  # 15 ints, 4 bytes of padding, size_t
 
 
 def plan(kind, sh, tune=None):
@@ -51,9 +51,13 @@ def test_planner_respects_limits(case, kind):
     rc, p = plan(kind, sh)
     assert rc == 0, _clib.last_error()
     assert 1 <= p["grid"] <= SMS
-    assert p["smem_bytes"] <= SMEM - 512
-    assert p["nb"] * p["ncb"] <= p["wpg"] * p["tpw"]
-    assert p["ns"] >= sh.r // 2 + 2
+    assert p["smem_bytes"] <= SMEM - 1024
+    if kind == _clib.WGRAD:   # tiles of 8 pixels x 2 rows
+        assert p["nb"] * p["ncb"] <= p["wpg"] * p["tpw"]
+    else:                     # blocks of 16 pixels x 1 row, (tpw + 1) // 2 per warp
+        assert p["ncb"] >= 2
+        assert p["nb"] * ((p["ncb"] + 1) // 2) <= p["wpg"] * ((p["tpw"] + 1) // 2)
+    assert p["ns"] >= 2 and p["pps"] in (1, 2)
     assert p["threads"] % 32 == 0 and p["threads"] <= 1024
     out_w = sh.w if kind == _clib.DGRAD else sh.q
     out_h = sh.h if kind == _clib.DGRAD else sh.p
@@ -80,7 +84,7 @@ def test_planner_rejects_bad_requests():
     assert rc != 0 and "positive" in _clib.last_error()
     rc, _ = plan(_clib.FPROP, Shape(1, 16, 8, 8), dict(wpg=7))
     assert rc != 0 and "variant" in _clib.last_error()
-    rc, _ = plan(_clib.FPROP, Shape(1, 64, 56, 56), dict(ns=16, nob=4))
+    rc, _ = plan(_clib.FPROP, Shape(1, 64, 56, 56), dict(ns=16, nob=4, pps=1))
     assert rc != 0 and "shared memory" in _clib.last_error()
     assert lib.spio_conv2d_gw8_plan_for(9, None, None, SMS, SMEM, None) != 0
 

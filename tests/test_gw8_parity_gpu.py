@@ -94,8 +94,9 @@ def test_every_tile_configuration(params):
         check_all(sh, params.has_bias, tune=cfg.as_tune(), what=("wgrad",))
 
 
-@pytest.mark.parametrize("tune", [dict(grid=1), dict(grid=3), dict(grid=7, ns=3, nob=1),
-                                  dict(grid=1000), dict(ncb=1), dict(ncb=2, nb=2)])
+@pytest.mark.parametrize("tune", [dict(grid=1), dict(grid=3), dict(grid=7, ns=2, nob=1),
+                                  dict(grid=7, ns=3, nob=1, pps=1), dict(grid=1000), dict(ncb=1),
+                                  dict(ncb=2, nb=2), dict(pps=1), dict(pps=2, grid=5)])
 def test_small_grids_rings_and_tiles(tune):
     """Few CTAs (long spans crossing image and chunk boundaries), more CTAs than SMs, the
     smallest ring, narrow tiles."""

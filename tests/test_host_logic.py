@@ -96,7 +96,8 @@ def test_configuration_spaces():
     assert len(fwd) > 20 and len(fwd) == len(set(fwd)) and len(bwd) == len(fwd)
     assert all(isinstance(c, Conv2dGw8Config) for c in fwd)
     assert all(isinstance(c, Conv2dGw8WgradConfig) for c in wg) and len(wg) > 10
-    assert all(c.nb * c.ncb <= c.wpg * c.tpw for c in fwd + wg)
+    assert all(c.nb * c.ncb <= c.wpg * c.tpw for c in wg)
+    assert all(c.nb * ((c.ncb + 1) // 2) <= c.wpg * ((c.tpw + 1) // 2) for c in fwd)
     tall = Conv2dGw8Params(n=4, c=32, h=20, w=20, padding=2, r=5, s=5)
     assert all(c.tpw <= 2 for c in conv2d_gw8_kernel_factory.configs(tall, B200_ATTRIBUTES))
 
@@ -108,7 +109,7 @@ def test_kernel_names_and_compile_without_device():
     assert f.get_kernel_name(igrad=True) == "spio_conv2d_gw8_dgrad"
     assert f.get_full_kernel_name(p) == "spio_conv2d_gw8_fprop__4n_64c_16h_32w_1py_1px_3r_3s_b"
     assert conv2d_gw8_wgrad_kernel_factory.get_kernel_name() == "spio_conv2d_gw8_wgrad"
-    k = f.make_kernel(p, Conv2dGw8Config(wpg=2, tpw=2), B200_ATTRIBUTES)
+    k = f.make_kernel(p, Conv2dGw8Config(wpg=2, tpw=2, pps=1), B200_ATTRIBUTES)
     k.compile(B200_ATTRIBUTES)
     assert k.plan["wpg"] == 2 and k.plan["tpw"] == 2 and k.launch_params.block == 576
     bad = f.make_kernel(p, Conv2dGw8Config(wpg=5), B200_ATTRIBUTES)
@@ -142,7 +143,7 @@ def test_performance_model_table_round_trip(tmp_path, monkeypatch):
     monkeypatch.setenv("SPIO_CACHE_DIR", str(tmp_path))
     pm = PerformanceModelCache()
     p = Conv2dGw8Params(n=128, c=64, h=56, w=56)
-    cfg = Conv2dGw8Config(wpg=2, tpw=4, ncb=7, nb=1, ns=8, nob=3)
+    cfg = Conv2dGw8Config(wpg=2, tpw=4, pps=1, ncb=7, nb=1, ns=8, nob=3)
     path = pm.record("spio_conv2d_gw8_fprop", "sm_100a", p, cfg)
     assert path.parent == tmp_path
     assert pm._table("spio_conv2d_gw8_fprop", "sm_100a")[p.encode()] == cfg.as_tune()
