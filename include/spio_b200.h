@@ -86,6 +86,26 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy,
                           const spio_gw8_shape* shape, const spio_gw8_tune* tune,
                           void* scratch, size_t scratch_bytes, void* stream);
 
+/* Weight gradient for callers that must not allocate device memory.  It has no counterpart
+ * in the reference.  Some callers cannot call cudaMalloc at the point where they need the
+ * gradient: code running inside another framework's memory pool with a fixed budget, a
+ * real-time loop that may not block on the allocator, a plugin that is handed tensors but no
+ * allocator.  This variant does the same computation as spio_conv2d_gw8_wgrad but takes its
+ * scratch from an 8 MiB buffer built into the library image (each GPU that loads the library
+ * holds those 8 MiB until the process exits), so the caller passes only inputs and output.
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - Shapes whose plan needs more than 8 MiB of scratch (3x3 filters on a 148-SM part need
+ *    5.2 MiB; 5x5 filters spread over all SMs need more) are rejected with an error; use
+ *    spio_conv2d_gw8_wgrad with your own scratch for those, or a smaller `tune->grid`.
+ *  - The first call on a device looks up the buffer's device address and sets kernel
+ *    attributes; make that first call before starting any stream capture.
+ *  - All calls share the one buffer.  Nothing in it has to be cleared (every part the reduce
+ *    step reads is overwritten first), but two calls that overlap on the GPU -- different
+ *    streams, or different host threads -- race on it; run them in stream order. */
+int spio_conv2d_gw8_wgrad_static(float* dw, const void* x, const void* dy,
+                                 const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                                 void* stream);
+
 /* Host-buffer variants: copy the operands to the device, run, copy the result back and
  * wait for it.  Device staging buffers are owned by the library and grow on demand.
  * Pinned host memory makes the copies asynchronous; pageable memory also works. */

@@ -54,6 +54,8 @@ SIGNATURES = {
     "spio_conv2d_gw8_wgrad": (
         c_int,
         [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p, c_size_t, c_void_p]),
+    "spio_conv2d_gw8_wgrad_static": (
+        c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
     "spio_conv2d_gw8_fprop_host": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune)]),
     "spio_conv2d_gw8_dgrad_host": (

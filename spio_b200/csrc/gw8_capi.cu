@@ -44,6 +44,12 @@ int fail_cuda(const char* what, cudaError_t e) {
 __device__ int g_status_word;
 
 constexpr int kMaxDevices = 64;
+
+// Scratch of the entry point that allocates nothing.  It is part of the library image, so
+// every GPU that loads the library sets this much memory aside until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+unsigned char* g_static_scratch_addr[kMaxDevices] = {};  // device address, per device
 constexpr int kFwdStaticSmem = 1024;   // >= static shared memory of the kernels
 constexpr int kAlignSlack = 1024;      // dynamic shared memory is re-aligned to 1 KiB
 
@@ -448,6 +454,39 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy, const spio_g
                           const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes,
                           void* stream) {
   return launch_wgrad(dw, x, dy, shape, tune, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+int spio_conv2d_gw8_wgrad_static(float* dw, const void* x, const void* dy,
+                                 const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                                 void* stream) {
+  int dev = 0;
+  GW8_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device ordinal out of range");
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;  // first call on a device: limits, kernel attributes (no allocation)
+  Plan pl;
+  if (make_plan(SPIO_GW8_WGRAD, shape, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
+  if (pl.scratch_bytes > kStaticScratchBytes) {
+    char buf[200];
+    snprintf(buf, sizeof buf,
+             "spio_conv2d_gw8_wgrad_static: this shape needs %zu bytes of scratch, the built-in "
+             "buffer holds %zu; use spio_conv2d_gw8_wgrad with caller-provided scratch",
+             pl.scratch_bytes, kStaticScratchBytes);
+    return fail(buf);
+  }
+  unsigned char* scratch = nullptr;
+  {
+    // In host code `g_static_scratch` is only a handle for the symbol; the address a kernel
+    // can use has to be asked for, once per device, with that device current.
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+      void* p = nullptr;
+      GW8_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+      g_static_scratch_addr[dev] = static_cast<unsigned char*>(p);
+    }
+    scratch = g_static_scratch_addr[dev];
+  }
+  return launch_wgrad(dw, x, dy, shape, tune, scratch, kStaticScratchBytes, (cudaStream_t)stream);
 }
 
 int spio_conv2d_gw8_fprop_host(void* y, const void* x, const void* w, const float* bias,
