@@ -188,14 +188,18 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
     constexpr bool ODD = (S & 1) != 0;  // last shift alone     -> x2 load,  k8 MMA
     constexpr int NLD = NQ + (ODD ? 1 : 0);
 
-    // per-lane byte offset inside a row of a slot for each load instruction
+    // per-lane byte offset of each load instruction: the NQ shift-pair loads address one row,
+    // the load of the odd last shift addresses both rows of a row pair
+    // {row 0: px 0-7, px 8-15; row 1: px 0-7, px 8-15}
     u32 ld_off[NLD];
 #pragma unroll
     for (int q = 0; q < NLD; ++q) {
-      const u32 mi = (u32)lane >> 3;                                      // matrix this lane addresses
-      const u32 sh = (ODD && q == NQ) ? (u32)(S - 1) : (u32)(2 * q) + (mi >> 1);  // column shift
-      const u32 px = 8u * (mi & 1u) + sh + l7;                            // pixel within the block
-      ld_off[q] = px * 128u + (((u32)grp ^ ((sh + l7) & 7u)) << 4);
+      const u32 mi = (u32)lane >> 3;  // matrix this lane addresses
+      const bool odd_col = ODD && q == NQ;
+      const u32 sh = odd_col ? (u32)(S - 1) : (u32)(2 * q) + (mi >> 1);  // column shift
+      const u32 px = 8u * (mi & 1u) + sh + l7;                           // pixel within the block
+      const u32 row = odd_col ? (mi >> 1) : 0u;
+      ld_off[q] = (row * (u32)g.bw + px) * 128u + (((u32)grp ^ ((sh + l7) & 7u)) << 4);
     }
     const u32 st_off = (8u * (((u32)lane >> 3) & 1u) + l7) * 128u + (((u32)grp ^ l7) << 4);
     const u32 in_row_bytes = g.in_pair_bytes >> 1;        // bw * 128
@@ -220,9 +224,10 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
     float bias0 = 0.f, bias1 = 0.f;
     bool grp_on = false;
     int cur_ck = -1;
-    // register window: [tile][physical row][shift pair][4] and, for odd S, [tile][row][2]
+    // register window: [tile][physical row][shift pair][4] and, for odd S, the last shift of
+    // both rows of a row pair: [tile][phase][4]
     u32 XQ[TPW][WIN][NQ > 0 ? NQ : 1][4];
-    u32 XP[TPW][WIN][2];
+    u32 XP[TPW][NPH][4];
 
     int slot = 0, ob = 0;
     u32 par = 0, opar = 0;
@@ -249,10 +254,10 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
                   ldmatrix_x4<false>(XQ[t][2 * PH + row][q][0], XQ[t][2 * PH + row][q][1],
                                      XQ[t][2 * PH + row][q][2], XQ[t][2 * PH + row][q][3],
                                      a + (u32)row * in_row_bytes + ld_off[q]);
-                if (ODD)
-                  ldmatrix_x2<false>(XP[t][2 * PH + row][0], XP[t][2 * PH + row][1],
-                                     a + (u32)row * in_row_bytes + ld_off[NLD - 1]);
               }
+              if (ODD)
+                ldmatrix_x4<false>(XP[t][PH][0], XP[t][PH][1], XP[t][PH][2], XP[t][PH][3],
+                                   a + ld_off[NLD - 1]);
             }
           }
         }
@@ -284,12 +289,24 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
                     // logical window row l = y + r (padded input row 2m + l) sits in
                     // physical row 2*((PH + 1 + l/2) % NPH) + (l & 1)
                     const int l = y + r;
-                    const int pr = 2 * ((PH + 1 + l / 2) % NPH) + (l & 1);
+                    const int pp = (PH + 1 + l / 2) % NPH;  // phase slot holding row l
+                    const int pr = 2 * pp + (l & 1);
 #pragma unroll
                     for (int q = 0; q < NQ; ++q)
                       mma_m16n8k16(acc, XQ[t][pr][q][0], XQ[t][pr][q][1], XQ[t][pr][q][2],
                                    XQ[t][pr][q][3], wreg[r * S + 2 * q], wreg[r * S + 2 * q + 1]);
-                    if (ODD) mma_m16n8k8(acc, XP[t][pr][0], XP[t][pr][1], wreg[r * S + S - 1]);
+                    if (ODD) {
+                      // Last column of taps: two vertically adjacent taps share one k16 MMA when
+                      // their input rows are the two rows of one slot, else a k8 MMA.
+                      const bool starts_pair = (l & 1) == 0 && r + 1 < Cfg::R;
+                      const bool in_prev_pair = (l & 1) == 1 && r >= 1;
+                      if (starts_pair)
+                        mma_m16n8k16(acc, XP[t][pp][0], XP[t][pp][1], XP[t][pp][2], XP[t][pp][3],
+                                     wreg[r * S + S - 1], wreg[(r + 1) * S + S - 1]);
+                      else if (!in_prev_pair)
+                        mma_m16n8k8(acc, XP[t][pp][2 * (l & 1)], XP[t][pp][2 * (l & 1) + 1],
+                                    wreg[r * S + S - 1]);
+                    }
                   }
                   const __half2 lo = __floats2half2_rn(acc[0], acc[1]);  // pixels 0-7 of the block
                   const __half2 hi = __floats2half2_rn(acc[2], acc[3]);  // pixels 8-15
