@@ -13,8 +13,11 @@ from typing import Dict, List, Sequence
 
 
 class GbtModel:
-    def __init__(self, features: List[str], base: float, rate: float, trees: List[list]):
+    def __init__(self, features: List[str], base: float, rate: float, trees: List[list],
+                 ranges: Dict[str, List[float]] = None):
         self.features = features
+        # [min, max] of every feature in the training rows; predictions outside are guesses
+        self.ranges = ranges or {}
         self.base = base
         self.rate = rate
         # tree = list of nodes; node = [feature_index, threshold, left, right] or [-1, value]
@@ -38,12 +41,22 @@ class GbtModel:
         return out
 
     # ------------------------------------------------------------ (de)serialisation
+    def covers(self, row: Dict[str, float], names: Sequence[str]) -> bool:
+        """True when the named features of ``row`` lie inside the training ranges."""
+        for name in names:
+            lo_hi = self.ranges.get(name)
+            if lo_hi is None or not lo_hi[0] <= float(row.get(name, 0.0)) <= lo_hi[1]:
+                return False
+        return True
+
     def to_json(self) -> dict:
-        return {"features": self.features, "base": self.base, "rate": self.rate, "trees": self.trees}
+        return {"features": self.features, "base": self.base, "rate": self.rate, "trees": self.trees,
+                "ranges": self.ranges}
 
     @classmethod
     def from_json(cls, obj: dict) -> "GbtModel":
-        return cls(list(obj["features"]), float(obj["base"]), float(obj["rate"]), obj["trees"])
+        return cls(list(obj["features"]), float(obj["base"]), float(obj["rate"]), obj["trees"],
+                   obj.get("ranges"))
 
     # ------------------------------------------------------------ training
     @classmethod
@@ -64,7 +77,8 @@ class GbtModel:
                 while node[0] >= 0:
                     node = tree[node[2] if x[node[0]] <= node[1] else node[3]]
                 resid[i] -= learning_rate * node[1]
-        return cls(features, base, learning_rate, trees)
+        ranges = {f: [min(x[i] for x in xs), max(x[i] for x in xs)] for i, f in enumerate(features)}
+        return cls(features, base, learning_rate, trees, ranges)
 
 
 def _grow(tree: List[list], xs, resid, idx: List[int], depth: int, min_leaf: int) -> int:

@@ -106,10 +106,11 @@ class PerformanceModelCache:
         if entry is not None:
             return kernel_factory.config_cls(**entry)
         model = self._model(kernel_name, arch)
-        if model is not None:
+        base = params_features(params, kernel_factory.per_model_skip_params)
+        # the model is trusted only for filter sizes and image extents it was trained on
+        if model is not None and model.covers(base, ("r", "s", "h", "w", "c")):
             configs = list(kernel_factory.configs(params, attr, **kernel_kwargs))
             if configs:
-                base = params_features(params, kernel_factory.per_model_skip_params)
                 rows = [dict(base, **{k: float(v) for k, v in c.as_tune().items()}) for c in configs]
                 pred = model.predict(rows)
                 return configs[min(range(len(configs)), key=pred.__getitem__)]
