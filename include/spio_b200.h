@@ -91,11 +91,11 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy,
  * gradient: code running inside another framework's memory pool with a fixed budget, a
  * real-time loop that may not block on the allocator, a plugin that is handed tensors but no
  * allocator.  This variant does the same computation as spio_conv2d_gw8_wgrad but takes its
- * scratch from an 8 MiB buffer built into the library image (each GPU that loads the library
- * holds those 8 MiB until the process exits), so the caller passes only inputs and output.
+ * scratch from an 4 MiB buffer built into the library image (each GPU that loads the library
+ * holds those 4 MiB until the process exits), so the caller passes only inputs and output.
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
- *  - Shapes whose plan needs more than 8 MiB of scratch (3x3 filters on a 148-SM part need
- *    5.2 MiB; 5x5 filters spread over all SMs need more) are rejected with an error; use
+ *  - Shapes whose plan needs more than 4 MiB of scratch (3x3 filters on a 148-SM part need
+ *    2.6 MiB; 5x5 filters spread over all SMs need more) are rejected with an error; use
  *    spio_conv2d_gw8_wgrad with your own scratch for those, or a smaller `tune->grid`.
  *  - The first call on a device looks up the buffer's device address and sets kernel
  *    attributes; make that first call before starting any stream capture.

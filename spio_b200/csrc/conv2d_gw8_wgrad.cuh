@@ -24,7 +24,9 @@
 namespace spio_b200 {
 
 // Scratch layout: [chunk][part][64 local out-channels][taps][8 in-channels] fp32 with
-// part = split * WPG + warp_sub, n_parts = n_split * WPG.
+// part = split index of the CTA, n_parts = n_split: the WPG warps of a group are summed
+// inside the CTA through shared memory before the partial is written.  CTAs that walk
+// several chunks (more chunks than CTAs) keep one part per warp instead, n_parts = n_split * WPG.
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
 conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
@@ -153,7 +155,12 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
     u32 par = 0;
     bool ok = true;
     bool full_seen = mbar_test_wait(full(0), 0u);
-    const int n_parts = g.n_split * WPG;
+    const bool cta_sum = WPG > 1 && !g.warp_parts;
+    const int n_parts = cta_sum ? g.n_split : g.n_split * WPG;
+    // Staging for the in-CTA sum of the WPG warps of a group.  It reuses the ring: a CTA
+    // that sums in shared memory works on one chunk only, so when it flushes every slot has
+    // been consumed and the load warp has nothing left to issue.
+    float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
 
     for (int ck = cl; ok && ck < g.n_chunks; ck += chunk_step) {
       const bool grp_on = (ck * 64 + grp * 8) < g.c;
@@ -242,18 +249,43 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
         }
       }
 
-      // Flush this warp's partial: acc[i] = {(tap 2i, c=g, k=2t), (.., k=2t+1),
-      //                                      (tap 2i+1, c=g, k=2t), (.., k=2t+1)}.
-      float* part = scratch + ((size_t)ck * n_parts + (size_t)(si * WPG + wsub)) * (64 * NT * 8);
-      const int kl = grp * 8 + 2 * t4;
+      // Sum the WPG warps of each group inside the CTA, then flush one partial per CTA:
+      // acc[i] = {(tap 2i, c=g, k=2t), (.., k=2t+1), (tap 2i+1, c=g, k=2t), (.., k=2t+1)}.
+      if (cta_sum) {
+        // every compute warp must have finished reading the ring before it is overwritten
+        asm volatile("bar.sync 1, %0;" ::"r"(NCW * 32) : "memory");
+        if (wsub > 0) {
+          float* dst = red + (size_t)((wsub - 1) * 8 + grp) * (NACC * 4 * 32) + lane;
 #pragma unroll
-      for (int i = 0; i < NACC; ++i) {
-        const int fa = 2 * i, fb = 2 * i + 1;
-        part[((kl + 0) * NT + fa) * 8 + gq] = acc[i][0];
-        part[((kl + 1) * NT + fa) * 8 + gq] = acc[i][1];
-        if (fb < NT) {
-          part[((kl + 0) * NT + fb) * 8 + gq] = acc[i][2];
-          part[((kl + 1) * NT + fb) * 8 + gq] = acc[i][3];
+          for (int i = 0; i < NACC; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dst[(i * 4 + e) * 32] = acc[i][e];
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(NCW * 32) : "memory");
+        if (wsub == 0) {
+#pragma unroll
+          for (int w = 1; w < WPG; ++w) {
+            const float* src = red + (size_t)((w - 1) * 8 + grp) * (NACC * 4 * 32) + lane;
+#pragma unroll
+            for (int i = 0; i < NACC; ++i)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) acc[i][e] += src[(i * 4 + e) * 32];
+          }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(NCW * 32) : "memory");  // red may be reused
+      }
+      if (wsub == 0 || !cta_sum) {
+        float* part = scratch + ((size_t)ck * n_parts + (size_t)(cta_sum ? si : si * WPG + wsub)) * (64 * NT * 8);
+        const int kl = grp * 8 + 2 * t4;
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) {
+          const int fa = 2 * i, fb = 2 * i + 1;
+          part[((kl + 0) * NT + fa) * 8 + gq] = acc[i][0];
+          part[((kl + 1) * NT + fa) * 8 + gq] = acc[i][1];
+          if (fb < NT) {
+            part[((kl + 0) * NT + fb) * 8 + gq] = acc[i][2];
+            part[((kl + 1) * NT + fb) * 8 + gq] = acc[i][3];
+          }
         }
       }
     }

@@ -47,7 +47,7 @@ constexpr int kMaxDevices = 64;
 
 // Scratch of the entry point that allocates nothing.  It is part of the library image, so
 // every GPU that loads the library sets this much memory aside until the process exits.
-constexpr size_t kStaticScratchBytes = 8u << 20;
+constexpr size_t kStaticScratchBytes = 4u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 unsigned char* g_static_scratch_addr[kMaxDevices] = {};  // device address, per device
 constexpr int kFwdStaticSmem = 1024;   // >= static shared memory of the kernels
@@ -138,6 +138,7 @@ struct Plan {
   int ns = 0, nob = 0, grid = 0, threads = 0;
   int smem = 0;
   size_t scratch_bytes = 0;
+  int n_parts = 1;  // wgrad partials per chunk
 };
 
 int check_shape(const spio_gw8_shape* sh) {
@@ -287,7 +288,12 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
     } else {
       pl.grid = ctas;
     }
-    pl.scratch_bytes = (size_t)g.n_chunks * g.n_split * v->wpg * 64 * sh->r * sh->s * 8 * sizeof(float);
+    // CTAs that walk several chunks cannot reuse the ring for the in-CTA sum
+    g.warp_parts = (pl.grid / g.n_split < g.n_chunks) ? 1 : 0;
+    const int red_need = (v->wpg - 1) * 8 * ((sh->r * sh->s + 1) / 2) * 4 * 32 * (int)sizeof(float);
+    if (red_need > pl.smem - kAlignSlack) g.warp_parts = 1;  // staging would not fit in the ring
+    pl.n_parts = g.n_split * (g.warp_parts ? v->wpg : 1);
+    pl.scratch_bytes = (size_t)g.n_chunks * pl.n_parts * 64 * sh->r * sh->s * 8 * sizeof(float);
   } else {
     pl.threads = v->fwd_threads;
     pl.grid = (int)(total < ctas ? total : ctas);
@@ -361,8 +367,7 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
   GW8_CUDA(cudaLaunchKernel(pl.v->wgrad_kernel, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
   const int taps = sh->r * sh->s;
   const int total_f4 = g.c * taps * 2;
-  conv2d_gw8_wgrad_reduce_kernel<256><<<cdiv(total_f4, 8), 256, 0, stream>>>(dw, sc, g.c, taps,
-                                                                       g.n_split * pl.v->wpg);
+  conv2d_gw8_wgrad_reduce_kernel<256><<<cdiv(total_f4, 8), 256, 0, stream>>>(dw, sc, g.c, taps, pl.n_parts);
   GW8_CUDA(cudaGetLastError());
   return 0;
 }

@@ -51,6 +51,8 @@ struct Gw8Geom {
   int ntiles;          // tiles per slot: nb * nblk (fprop/dgrad) or nb * ncb (wgrad); <= WPG * TPW
   int dgrad;           // 1: weights are used transposed and flipped
   int n_split;         // wgrad: CTAs that share one chunk
+  int warp_parts;      // wgrad: 1 = every compute warp writes its own partial (CTAs that walk
+                       // several chunks), 0 = the warps of a group are summed inside the CTA
   // byte sizes derived from the above (kept here so that the kernels read them from the
   // constant bank instead of holding them in registers); pps = row pairs per slot
   unsigned in_pair_bytes;    // 2 rows of one image of the streamed operand: 2*bw*128
