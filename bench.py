@@ -36,9 +36,18 @@ sys.path.insert(0, str(ROOT))
 GLOBAL_BATCH = 2048
 C, H, W, R, S, PAD = 64, 56, 56, 3, 3, 1
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one forward-kernel launch divided by its
-# algorithmic bytes, from the ncu capture summarised in profiles/ (None until captured).
-FWD_DRAM_TRAFFIC_RATIO = None
+# DRAM traffic of one forward-kernel launch, from the ncu capture at N=512 summarised in
+# profiles/conv2d_gw8_fwd_kernel__c64_56x56_3x3_n512.md: reads are 1.010 x the input bytes
+# (halo rows at span ends); writes are the output bytes minus ~50 MB that are still dirty in
+# the 126 MB L2 when the kernel ends.  Reads and writes grow with the batch, the L2 residue
+# does not, so a launch at another batch is estimated as below.
+FWD_DRAM_READ_RATIO = 1.010
+FWD_L2_RESIDUE_BYTES = 50.1e6
+
+
+def fwd_dram_traffic(algorithmic: int) -> float:
+    half = algorithmic / 2.0
+    return FWD_DRAM_READ_RATIO * half + max(half - FWD_L2_RESIDUE_BYTES, 0.0)
 
 
 def algorithmic_bytes(n: int) -> int:
@@ -278,7 +287,8 @@ def run_ours(args) -> None:
             "roofline": {"bound": "hbm", "kernel": "conv2d_gw8_fwd_kernel (fprop launch)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind + " copy bandwidth",
                          "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": (FWD_DRAM_TRAFFIC_RATIO * b_one if FWD_DRAM_TRAFFIC_RATIO else None),
+                         "traffic": fwd_dram_traffic(b_one),
+                         "traffic_source": "ncu capture at N=512 scaled to this batch (profiles/)",
                          "algorithmic_bytes_per_launch": b_one},
             "e2e": None if not e2e_steps else {"value": step_bytes_all / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "ms_per_step": e2e_ms, "steps": e2e_steps,
