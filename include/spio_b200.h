@@ -126,6 +126,52 @@ int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_t
 int spio_conv2d_gw8_plan_for(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
                              int sm_count, int smem_optin_bytes, spio_gw8_plan_info* info);
 
+/* ---- just-in-time path --------------------------------------------------------------
+ * NVRTC compilation and driver-API module load / launch, for kernels specialised per layer
+ * shape and for tile configurations that are not compiled into the library.  Replaces the
+ * reference's spio/cuda/nvrtc_ctypes.py:152-217 and spio/compiler/compile.py:22-77 (compile)
+ * and spio/cuda/driver.pyx:126-273 (Module, Function.launch). */
+int spio_jit_set_nvrtc_path(const char* path);           /* where libnvrtc.so.12 lives */
+int spio_jit_nvrtc_version(int* major, int* minor);
+/* Compiles `source` (options as for nvrtcCompileProgram, e.g. "-arch=sm_100a"; headers are
+ * given in memory).  On success *cubin / *cubin_size hold the image; *log (if not NULL)
+ * receives the compiler log, which contains the register / spill report when
+ * "--ptxas-options=-v" is among the options.  Free both with spio_jit_free. */
+int spio_jit_compile(const char* source, const char* file_name, const char* const* options, int n_options,
+                     const char* const* header_names, const char* const* header_sources, int n_headers,
+                     void** cubin, size_t* cubin_size, char** log);
+void spio_jit_free(void* p);
+int spio_module_load(const void* cubin, void** module);
+int spio_module_unload(void* module);
+int spio_module_get_function(void* module, const char* name, void** function);
+int spio_function_set_max_dynamic_smem(void* function, int bytes);
+/* which: 0 registers per thread, 1 local (spill) bytes, 2 static shared bytes, 3 max threads */
+int spio_function_get_attribute(void* function, int which, int* value);
+/* args: one pointer per kernel parameter, as for cuLaunchKernel */
+int spio_function_launch(void* function, int grid, int block, int smem_bytes, void* stream, void** args);
+
+/* Everything a just-in-time compiled gw8 kernel needs for one launch: the two tensor maps
+ * and the geometry it takes by value, the launch dimensions and the status word.  Kernel
+ * parameter lists:
+ *   fprop / dgrad: (in_map, out_map, geom, const half* w, const float* bias, int ns, int nob, int* status)
+ *   wgrad:         (in_map, out_map, geom, float* scratch, int ns, int* status), followed by
+ *                  spio_conv2d_gw8_wgrad_reduce(dw, scratch, c, r*s, n_parts, stream). */
+typedef struct spio_gw8_launch {
+  unsigned long long in_map[16];   /* CUtensorMap of the streamed operand (x; dy for dgrad) */
+  unsigned long long out_map[16];  /* CUtensorMap of the tiled operand (y; dx; dy for wgrad) */
+  int geom[32];                    /* kernel-side geometry struct, opaque */
+  int ns, nob, grid, threads, smem_bytes, n_parts;
+  size_t scratch_bytes;
+  int* status;
+} spio_gw8_launch;
+/* tune->wpg, tpw, pps must be given; they need not be a compiled variant.  plan_jit is the
+ * host-only planner for such a configuration (cf. spio_conv2d_gw8_plan_for). */
+int spio_conv2d_gw8_plan_jit(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, int sm_count,
+                             int smem_optin_bytes, spio_gw8_plan_info* info);
+int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                                   const void* streamed, const void* tiled, spio_gw8_launch* out);
+int spio_conv2d_gw8_wgrad_reduce(float* dw, const float* scratch, int c, int taps, int n_parts, void* stream);
+
 /* Number of compiled (r, s, wpg, tpw, pps) variants, and the i-th one. */
 int spio_conv2d_gw8_num_variants(void);
 int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw, int* pps);

@@ -8,7 +8,7 @@ or fails to load, every operator raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_size_t, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_size_t, c_ulonglong, c_void_p
 from pathlib import Path
 from typing import Optional
 
@@ -44,6 +44,21 @@ class PlanInfo(Structure):
         return {name: getattr(self, name) for name, _ in self._fields_}
 
 
+class Launch(Structure):
+    """struct spio_gw8_launch: tensor maps, geometry and launch dimensions of one call of a
+    just-in-time compiled kernel."""
+
+    _fields_ = [
+        ("in_map", c_ulonglong * 16),
+        ("out_map", c_ulonglong * 16),
+        ("geom", c_int * 32),
+        ("ns", c_int), ("nob", c_int), ("grid", c_int), ("threads", c_int),
+        ("smem_bytes", c_int), ("n_parts", c_int),
+        ("scratch_bytes", c_size_t),
+        ("status", c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); one entry per symbol declared in include/spio_b200.h
 SIGNATURES = {
     "spio_conv2d_gw8_fprop": (
@@ -65,6 +80,24 @@ SIGNATURES = {
     "spio_conv2d_gw8_plan": (c_int, [c_int, POINTER(Shape), POINTER(Tune), POINTER(PlanInfo)]),
     "spio_conv2d_gw8_plan_for": (
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),
+    "spio_jit_set_nvrtc_path": (c_int, [c_char_p]),
+    "spio_jit_nvrtc_version": (c_int, [POINTER(c_int), POINTER(c_int)]),
+    "spio_jit_compile": (
+        c_int,
+        [c_char_p, c_char_p, POINTER(c_char_p), c_int, POINTER(c_char_p), POINTER(c_char_p), c_int,
+         POINTER(c_void_p), POINTER(c_size_t), POINTER(c_void_p)]),
+    "spio_jit_free": (None, [c_void_p]),
+    "spio_module_load": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "spio_module_unload": (c_int, [c_void_p]),
+    "spio_module_get_function": (c_int, [c_void_p, c_char_p, POINTER(c_void_p)]),
+    "spio_function_set_max_dynamic_smem": (c_int, [c_void_p, c_int]),
+    "spio_function_get_attribute": (c_int, [c_void_p, c_int, POINTER(c_int)]),
+    "spio_function_launch": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, POINTER(c_void_p)]),
+    "spio_conv2d_gw8_plan_jit": (
+        c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),
+    "spio_conv2d_gw8_prepare_launch": (
+        c_int, [c_int, POINTER(Shape), POINTER(Tune), c_void_p, c_void_p, POINTER(Launch)]),
+    "spio_conv2d_gw8_wgrad_reduce": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "spio_conv2d_gw8_num_variants": (c_int, []),
     "spio_conv2d_gw8_variant": (
         c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),

@@ -28,12 +28,13 @@
 
 namespace spio_b200 {
 
+// The kernel body is a device function so that both the ahead-of-time instantiations and
+// the just-in-time wrappers (one extern "C" kernel per layer shape) can share it.
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, 1)
-conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
-                      const __grid_constant__ TensorMap out_map, const Gw8Geom g,
-                      const __half* __restrict__ wgt, const float* __restrict__ bias,
-                      int ns, int nob, int* __restrict__ status) {
+__device__ __forceinline__ void
+conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8Geom& g,
+                    const __half* __restrict__ wgt, const float* __restrict__ bias, int ns, int nob,
+                    int* __restrict__ status) {
   constexpr int S = Cfg::S, WPG = Cfg::WPG, TPW = Cfg::TPW, PPS = Cfg::PPS;
   constexpr int E = Cfg::E, WIN = Cfg::WIN, NT = Cfg::NT, NCW = Cfg::NCW;
   constexpr int NPH = WIN / 2;  // the window rotates by one row pair per sub-step
@@ -383,6 +384,15 @@ conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
     if (threadIdx.x == 0) atomicExch(status, (int)GW8_WAIT_TIMEOUT);
   }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+conv2d_gw8_fwd_kernel(const __grid_constant__ TensorMap in_map,
+                      const __grid_constant__ TensorMap out_map, const Gw8Geom g,
+                      const __half* __restrict__ wgt, const float* __restrict__ bias,
+                      int ns, int nob, int* __restrict__ status) {
+  conv2d_gw8_fwd_body<Cfg>(in_map, out_map, g, wgt, bias, ns, nob, status);
 }
 
 }  // namespace spio_b200

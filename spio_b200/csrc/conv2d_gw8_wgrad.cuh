@@ -27,11 +27,12 @@ namespace spio_b200 {
 // part = split index of the CTA, n_parts = n_split: the WPG warps of a group are summed
 // inside the CTA through shared memory before the partial is written.  CTAs that walk
 // several chunks (more chunks than CTAs) keep one part per warp instead, n_parts = n_split * WPG.
+// The kernel body is a device function so that both the ahead-of-time instantiations and
+// the just-in-time wrappers (one extern "C" kernel per layer shape) can share it.
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
-conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
-                        const __grid_constant__ TensorMap dy_map, const Gw8Geom g,
-                        float* __restrict__ scratch, int ns, int* __restrict__ status) {
+__device__ __forceinline__ void
+conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8Geom& g,
+                      float* __restrict__ scratch, int ns, int* __restrict__ status) {
   constexpr int S = Cfg::S, WPG = Cfg::WPG, TPW = Cfg::TPW, PPS = Cfg::PPS;
   constexpr int E = Cfg::E, WIN = Cfg::WIN, NT = Cfg::NT, NCW = Cfg::NCW;
   constexpr int NPH = WIN / 2;
@@ -296,6 +297,14 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
     if (threadIdx.x == 0) atomicExch(status, (int)GW8_WAIT_TIMEOUT);
   }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
+conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
+                        const __grid_constant__ TensorMap dy_map, const Gw8Geom g,
+                        float* __restrict__ scratch, int ns, int* __restrict__ status) {
+  conv2d_gw8_wgrad_body<Cfg>(x_map, dy_map, g, scratch, ns, status);
 }
 
 // dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], added in a

@@ -29,6 +29,10 @@ int fail(const std::string& msg) {
   return 1;
 }
 
+}  // namespace
+int jit_fail(const std::string& msg) { return fail(msg); }  // used by jit_driver.cpp
+namespace {
+
 int fail_cuda(const char* what, cudaError_t e) {
   return fail(std::string("CUDA error: ") + cudaGetErrorString(e) + " (" + what + ")");
 }
@@ -157,7 +161,7 @@ int check_shape(const spio_gw8_shape* sh) {
 // The plan needs only the SM count and the shared-memory limit, so it can be computed
 // (and unit-tested) without a device.
 int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
-              const std::vector<Gw8Variant>& variants, Plan* plan) {
+              const std::vector<Gw8Variant>& variants, Plan* plan, const Gw8Variant* forced = nullptr) {
   if (check_shape(sh)) return 1;
   static const spio_gw8_tune kAuto = {0, 0, 0, 0, 0, 0, 0, 0};
   const spio_gw8_tune& t = tune ? *tune : kAuto;
@@ -167,7 +171,7 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
   // Unless the caller asks otherwise, the forward kernel streams one row pair per slot
   // (its register window then fits without spills) and the weight-gradient kernel two.
   const int default_pps = kind == SPIO_GW8_WGRAD ? 2 : 1;
-  const Gw8Variant* v = nullptr;
+  const Gw8Variant* v = forced;
   for (int pass = 0; pass < 2 && v == nullptr; ++pass) {
     for (const Gw8Variant& cand : variants) {
       if (cand.r != sh->r || cand.s != sh->s) continue;
@@ -553,6 +557,74 @@ int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy, const s
     return 1;
   GW8_CUDA(cudaMemcpyAsync(dw, st->buf[2], wb, cudaMemcpyDeviceToHost, st->stream));
   GW8_CUDA(cudaStreamSynchronize(st->stream));
+  return 0;
+}
+
+// The variant record of a kernel that is compiled just in time for (r, s, wpg, tpw, pps).
+static int jit_variant(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, Gw8Variant* v) {
+  if (tune == nullptr) return fail("a just-in-time kernel needs a tile configuration");
+  if (kind < SPIO_GW8_FPROP || kind > SPIO_GW8_WGRAD) return fail("unknown kind");
+  if (tune->wpg < 1 || tune->wpg > 3 || tune->tpw < 1 || tune->tpw > 8 || tune->pps < 1 || tune->pps > 2)
+    return fail("a just-in-time kernel needs explicit wpg (1..3), tpw (1..8) and pps (1..2)");
+  if (check_shape(shape)) return 1;
+  *v = Gw8Variant{};
+  v->r = shape->r, v->s = shape->s, v->wpg = tune->wpg, v->tpw = tune->tpw, v->pps = tune->pps;
+  v->fwd_threads = (8 * tune->wpg + 2) * 32;
+  v->wgrad_threads = (8 * tune->wpg + 1) * 32;
+  return 0;
+}
+
+int spio_conv2d_gw8_plan_jit(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, int sm_count,
+                             int smem_optin_bytes, spio_gw8_plan_info* info) {
+  if (info == nullptr) return fail("info is NULL");
+  if (sm_count <= 0 || smem_optin_bytes <= 0) return fail("sm_count and smem_optin_bytes must be positive");
+  Gw8Variant v;
+  if (jit_variant(kind, shape, tune, &v)) return 1;
+  Plan pl;
+  if (make_plan(kind, shape, tune, sm_count, smem_optin_bytes, g_variants, &pl, &v)) return 1;
+  fill_info(pl, info);
+  return 0;
+}
+
+int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
+                                   const void* streamed, const void* tiled, spio_gw8_launch* out) {
+  static_assert(sizeof(Gw8Geom) <= sizeof(out->geom), "geometry blob too small");
+  static_assert(sizeof(CUtensorMap) == sizeof(out->in_map), "tensor map size");
+  if (out == nullptr) return fail("NULL argument");
+  if (streamed == nullptr || tiled == nullptr) return fail("NULL tensor pointer");
+  Gw8Variant v;
+  if (jit_variant(kind, shape, tune, &v)) return 1;
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;
+  Plan pl;
+  if (make_plan(kind, shape, tune, d->sms, d->smem_optin, g_variants, &pl, &v)) return 1;
+  const Gw8Geom& g = pl.g;
+  memset(out, 0, sizeof *out);
+  CUtensorMap a, b;
+  if (encode_map(&a, streamed, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * v.pps, g.nb)) return 1;
+  if (encode_map(&b, tiled, g.c, g.out_w, g.out_h, g.n, g.wt, kind == SPIO_GW8_WGRAD ? 2 * v.pps : 2, g.nb))
+    return 1;
+  memcpy(out->in_map, &a, sizeof a);
+  memcpy(out->out_map, &b, sizeof b);
+  memcpy(out->geom, &g, sizeof g);
+  out->ns = pl.ns;
+  out->nob = pl.nob;
+  out->grid = pl.grid;
+  out->threads = pl.threads;
+  out->smem_bytes = pl.smem;
+  out->n_parts = pl.n_parts;
+  out->scratch_bytes = pl.scratch_bytes;
+  out->status = d->status;
+  return 0;
+}
+
+int spio_conv2d_gw8_wgrad_reduce(float* dw, const float* scratch, int c, int taps, int n_parts, void* stream) {
+  if (dw == nullptr || scratch == nullptr || c <= 0 || c % 8 || taps <= 0 || n_parts <= 0)
+    return fail("bad argument");
+  const int total_f4 = c * taps * 2;
+  conv2d_gw8_wgrad_reduce_kernel<256><<<cdiv(total_f4, 8), 256, 0, (cudaStream_t)stream>>>(dw, scratch, c, taps,
+                                                                                           n_parts);
+  GW8_CUDA(cudaGetLastError());
   return 0;
 }
 

@@ -1,0 +1,153 @@
+"""A kernel compiled just in time with NVRTC and launched through the driver API.
+
+Mirrors the reference's kernel life cycle (spio/kernels/kernel.py:37-157): ``compile()``
+turns generated source into a cubin, ``load()`` loads the cubin into the device's primary
+context and looks the function up by its full name, ``launch()`` passes the tensors.  The
+instantiated tile configuration does not have to be one of those built into the library,
+which is what the autotuner uses to search beyond them.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _clib
+from ..util.tensor_format import check_channels_last
+from .kernel import KIND_BY_NAME, Kernel
+from .launch_params import LaunchParams
+
+
+class JitKernel(Kernel):
+    def __init__(self, kernel_name: str, base_name: str, params, config=None,
+                 args_checker=check_channels_last):
+        super().__init__(kernel_name, base_name, params, config, args_checker)
+        self.cubin: Optional[bytes] = None
+        self.compile_log: str = ""
+        self.module = None
+        self.function = None
+        self._arch = None
+
+    # ------------------------------------------------------------ life cycle
+    def _resolve_tune(self, attr) -> None:
+        """Fill wpg / tpw / pps from the launch planner when the configuration leaves them open."""
+        t = self._tune
+        if t is not None and t.wpg > 0 and t.tpw > 0 and t.pps > 0:
+            return
+        info = _clib.PlanInfo()
+        _clib.check(_clib.load().spio_conv2d_gw8_plan_for(
+            self.kind, ctypes.byref(self._shape), self._tune_ref(), attr.multiprocessor_count,
+            attr.max_shared_memory_per_block_optin, ctypes.byref(info)), self.kernel_name)
+        if t is None:
+            t = self._tune = _clib.Tune()
+        t.wpg, t.tpw, t.pps = info.wpg, info.tpw, info.pps
+
+    @property
+    def function_name(self) -> str:
+        t = self._tune
+        return f"{self.kernel_name}__wpg{t.wpg}_tpw{t.tpw}_pps{t.pps}"
+
+    @property
+    def source(self) -> str:
+        from ..compiler.compile_kernel import kernel_source
+
+        t = self._tune
+        return kernel_source(self.function_name, self.kind == _clib.WGRAD, self.params.r, self.params.s,
+                             t.wpg, t.tpw, t.pps)
+
+    def compile(self, device_attr=None) -> None:
+        from ..compiler import flags
+        from ..compiler.compile_kernel import compile_kernel
+        from ..cuda.driver import B200_ATTRIBUTES
+
+        attr = device_attr or B200_ATTRIBUTES
+        try:
+            self._resolve_tune(attr)
+            info = _clib.PlanInfo()
+            _clib.check(_clib.load().spio_conv2d_gw8_plan_jit(
+                self.kind, ctypes.byref(self._shape), self._tune_ref(), attr.multiprocessor_count,
+                attr.max_shared_memory_per_block_optin, ctypes.byref(info)), self.kernel_name)
+            self.plan = info.as_dict()
+            self._arch = attr.compute_capability
+            self.cubin, self.compile_log = compile_kernel(
+                self.source, source_name=self.function_name + ".cu", arch=self._arch,
+                debug=flags.debug.get(), lineinfo=flags.lineinfo.get(), return_log=True)
+        except Exception as exc:
+            raise ValueError(f"Error in kernel {self}: {exc}") from exc
+
+    def load(self, device_ordinal: int = 0, clear_cubin: bool = True) -> None:
+        from ..compiler.compile_kernel import load_kernel
+
+        if not torch.cuda.is_available():
+            raise ValueError("CUDA error: no CUDA device is available")
+        if self.cubin is None:
+            raise ValueError(f"Error in kernel {self}: compile() must be called before load()")
+        self._lib = _clib.load()
+        self._device_ordinal = device_ordinal
+        self.module, self.function = load_kernel(self.function_name, self.cubin, device_ordinal)
+        self.function.set_max_dynamic_shared_memory_size(self.plan["smem_bytes"])
+        self._scratch_bytes = int(self.plan["scratch_bytes"])
+        if clear_cubin:
+            self.cubin = None
+
+    def unload(self) -> None:
+        self.function = None
+        if self.module is not None:
+            self.module.unload()
+            self.module = None
+        super().unload()
+
+    @property
+    def resource_usage(self) -> dict:
+        """Registers per thread, spill bytes and static shared memory of the loaded function."""
+        if self.function is None:
+            raise ValueError(f"Error in kernel {self}: kernel is not loaded")
+        return {k: self.function.get_attribute(k) for k in ("num_regs", "local_size_bytes", "shared_size_bytes")}
+
+    # ------------------------------------------------------------ launch
+    def launch(self, *args) -> None:
+        if self.function is None:
+            raise ValueError(f"Error in kernel {self}: kernel is not loaded")
+        try:
+            self._args_checker(args)
+            dev = args[0].device
+            with torch.cuda.device(dev):
+                stream = torch.cuda.current_stream(dev).cuda_stream
+                # fprop (y, x, w, bias), dgrad (dx, dy, w, None), wgrad (dw, x, dy):
+                # the streamed operand is args[1]; the tiled one is the result, or dy for wgrad
+                tiled = args[2] if self.kind == _clib.WGRAD else args[0]
+                lp = _clib.Launch()
+                _clib.check(self._lib.spio_conv2d_gw8_prepare_launch(
+                    self.kind, ctypes.byref(self._shape), self._tune_ref(), args[1].data_ptr(),
+                    tiled.data_ptr(), ctypes.byref(lp)))
+                status = ctypes.c_void_p(lp.status)
+                if self.kind == _clib.WGRAD:
+                    scratch = torch.empty(lp.scratch_bytes, dtype=torch.uint8, device=dev)
+                    kargs = [lp.in_map, lp.out_map, lp.geom, scratch, int(lp.ns), status]
+                else:
+                    if args[2].data_ptr() % 16:
+                        raise ValueError("weight pointer must be 16-byte aligned")
+                    kargs = [lp.in_map, lp.out_map, lp.geom, args[2], args[3], int(lp.ns), int(lp.nob), status]
+                self.function.launch(lp.grid, lp.threads, kargs, shared_mem_bytes=lp.smem_bytes, stream=stream)
+                if self.kind == _clib.WGRAD:
+                    _clib.check(self._lib.spio_conv2d_gw8_wgrad_reduce(
+                        args[0].data_ptr(), scratch.data_ptr(), self.params.c, self.params.r * self.params.s,
+                        lp.n_parts, stream))
+        except Exception as exc:
+            raise ValueError(f"Error in kernel {self}: {exc}") from exc
+
+    __call__ = launch
+
+    @property
+    def launch_params(self) -> Optional[LaunchParams]:
+        if self.plan is None:
+            return None
+        return LaunchParams(self.plan["grid"], self.plan["threads"], self.plan["smem_bytes"])
+
+    def __repr__(self) -> str:
+        return f"{self.kernel_name} {self.config} (jit)"
+
+
+__all__ = ["JitKernel", "KIND_BY_NAME"]

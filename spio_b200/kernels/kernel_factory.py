@@ -14,6 +14,20 @@ from ..util.tensor_format import check_channels_last
 from .kernel import Kernel, get_full_kernel_name
 
 
+def _wants_jit(params, config) -> bool:
+    from ..compiler import flags
+
+    if flags.jit.get():
+        return True
+    tune = config.as_tune() if config is not None else {}
+    wpg, tpw, pps = (tune.get(k, 0) for k in ("wpg", "tpw", "pps"))
+    if not (wpg and tpw and pps):
+        return False
+    from .conv2d_gw8_kernel import compiled_variants
+
+    return (wpg, tpw, pps) not in compiled_variants(params.r, params.s)
+
+
 class KernelFactory:
     def __init__(self, params_cls=None, config_cls=None, stats_cls=None,
                  kernel_name: Union[str, Callable[..., str]] = None,
@@ -55,10 +69,18 @@ class KernelFactory:
         model, made and loaded."""
         return self.get_kernel_cache(**kwargs).get(self, params, device, **kwargs)
 
-    def make_kernel(self, params, config, device_attr=None, **kwargs) -> Kernel:
+    def make_kernel(self, params, config, device_attr=None, jit: Optional[bool] = None, **kwargs) -> Kernel:
+        """``jit=True`` compiles the kernel with NVRTC, ``jit=False`` uses a variant built into
+        the library; the default is just in time only when SPIO_JIT is set or the
+        configuration's (wpg, tpw, pps) is not among the built-in variants."""
         del device_attr
-        return Kernel(self.get_full_kernel_name(params, **kwargs), self.get_kernel_name(**kwargs),
-                      params=params, config=config, args_checker=self._args_checker)
+        if jit is None:
+            jit = _wants_jit(params, config)
+        cls = Kernel
+        if jit:
+            from .jit_kernel import JitKernel as cls
+        return cls(self.get_full_kernel_name(params, **kwargs), self.get_kernel_name(**kwargs),
+                   params=params, config=config, args_checker=self._args_checker)
 
     def __repr__(self) -> str:
         return f"KernelFactory({self._kernel_name if isinstance(self._kernel_name, str) else 'conv2d_gw8'})"
