@@ -86,6 +86,19 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy,
                           const spio_gw8_shape* shape, const spio_gw8_tune* tune,
                           void* scratch, size_t scratch_bytes, void* stream);
 
+/* Both gradients of one layer in one call (dx or dw may be NULL to skip it).  Launches the
+ * weight-gradient kernel, its reduce kernel and the input-gradient kernel back to back with
+ * programmatic dependent launch: the input-gradient kernel shares no output with the other
+ * two, so its CTAs take over SMs as theirs finish instead of waiting for the whole grid to
+ * drain; dw is complete first, and `dw_ready` (a cudaEvent_t, or NULL) is recorded at that
+ * point, so a data-parallel caller can make its communication stream wait for the event and
+ * all-reduce dw while the input gradient is still being computed.  Replaces the two launches of the reference's
+ * backward operator (spio/functional/conv2d_gw8_function.py:93-147). */
+int spio_conv2d_gw8_backward(void* dx, float* dw, const void* x, const void* dy, const void* w,
+                             const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
+                             const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes,
+                             void* stream, void* dw_ready);
+
 /* Weight gradient for callers that must not allocate device memory.  It has no counterpart
  * in the reference.  Some callers cannot call cudaMalloc at the point where they need the
  * gradient: code running inside another framework's memory pool with a fixed budget, a

@@ -69,6 +69,10 @@ SIGNATURES = {
     "spio_conv2d_gw8_wgrad": (
         c_int,
         [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p, c_size_t, c_void_p]),
+    "spio_conv2d_gw8_backward": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), POINTER(Tune),
+         c_void_p, c_size_t, c_void_p, c_void_p]),
     "spio_conv2d_gw8_wgrad_static": (
         c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
     "spio_conv2d_gw8_fprop_host": (

@@ -67,6 +67,11 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
     mbar_fence_init();
   }
   __syncthreads();
+  // Everything above touches only shared memory and may overlap the tail of the preceding
+  // kernel.  Dependents are released only after the wait, so a chain of such launches never
+  // runs ahead of the work that precedes its first kernel.
+  if (!g.independent) grid_dependency_wait();
+  grid_dependency_launch_dependents();
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;

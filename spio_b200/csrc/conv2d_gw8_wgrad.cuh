@@ -62,6 +62,11 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     mbar_fence_init();
   }
   __syncthreads();
+  // Everything above touches only shared memory and may overlap the tail of the preceding
+  // kernel.  Dependents are released only after the wait, so a chain of such launches never
+  // runs ahead of the work that precedes its first kernel.
+  if (!g.independent) grid_dependency_wait();
+  grid_dependency_launch_dependents();
 
   // CTA b works on split `si` of chunks cl, cl + chunk_step, ...
   const int si = blockIdx.x % g.n_split;
@@ -317,6 +322,9 @@ __global__ void __launch_bounds__(THREADS)
 conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__ scratch, int c,
                                int taps, int n_parts) {
   __shared__ float4 red[8][8];
+  // Let an independent successor take SMs as they become free, then wait for the partials.
+  grid_dependency_launch_dependents();
+  grid_dependency_wait();
   const int cx = threadIdx.x & 7;
   const int pl = (threadIdx.x >> 3) & 3;
   const int wy = threadIdx.x >> 5;

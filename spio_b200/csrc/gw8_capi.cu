@@ -329,13 +329,43 @@ int encode_map(CUtensorMap* m, const void* ptr, int c, int w, int h, int n, int 
 
 static_assert(sizeof(TensorMap) == sizeof(CUtensorMap), "tensor map size");
 
+// SPIO_PDL=0 turns programmatic dependent launch off (every kernel then starts only after
+// the preceding one has drained).
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SPIO_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+// Launches with the programmatic-stream-serialization attribute: the kernel's CTAs may take
+// SMs while the preceding kernel of the stream drains, and the kernel itself waits
+// (griddepcontrol.wait) before it touches global memory.
+int launch_kernel(const void* func, int grid, int threads, size_t smem, cudaStream_t stream, void** args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  GW8_CUDA(cudaLaunchKernelExC(&cfg, func, args));
+  return 0;
+}
+
 int launch_fwd(int kind, void* out, const void* in, const void* w, const float* bias,
-               const spio_gw8_shape* sh, const spio_gw8_tune* tune, cudaStream_t stream) {
+               const spio_gw8_shape* sh, const spio_gw8_tune* tune, cudaStream_t stream,
+               bool independent = false) {
   if (out == nullptr || in == nullptr || w == nullptr) return fail("NULL tensor pointer");
   const DeviceInfo* d = nullptr;
   if (device_info(&d)) return 1;
   Plan pl;
   if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
+  pl.g.independent = (independent && pdl_enabled()) ? 1 : 0;
   const Gw8Geom& g = pl.g;
   CUtensorMap in_map, out_map;
   if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
@@ -345,8 +375,14 @@ int launch_fwd(int kind, void* out, const void* in, const void* w, const float* 
   int ns = pl.ns, nob = pl.nob;
   int* status = d->status;
   void* args[] = {&in_map, &out_map, (void*)&g, &wp, &bias, &ns, &nob, &status};
-  GW8_CUDA(cudaLaunchKernel(pl.v->fwd_kernel, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
-  return 0;
+  return launch_kernel(pl.v->fwd_kernel, pl.grid, pl.threads, pl.smem, stream, args);
+}
+
+int launch_reduce(float* dw, const float* scratch, int c, int taps, int n_parts, cudaStream_t stream) {
+  const int total_f4 = c * taps * 2;
+  void* args[] = {&dw, &scratch, &c, &taps, &n_parts};
+  return launch_kernel(reinterpret_cast<const void*>(&conv2d_gw8_wgrad_reduce_kernel<256>), cdiv(total_f4, 8), 256,
+                       0, stream, args);
 }
 
 int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape* sh,
@@ -368,12 +404,8 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
   int ns = pl.ns;
   int* status = d->status;
   void* args[] = {&x_map, &dy_map, (void*)&g, &sc, &ns, &status};
-  GW8_CUDA(cudaLaunchKernel(pl.v->wgrad_kernel, dim3(pl.grid), dim3(pl.threads), args, pl.smem, stream));
-  const int taps = sh->r * sh->s;
-  const int total_f4 = g.c * taps * 2;
-  conv2d_gw8_wgrad_reduce_kernel<256><<<cdiv(total_f4, 8), 256, 0, stream>>>(dw, sc, g.c, taps, pl.n_parts);
-  GW8_CUDA(cudaGetLastError());
-  return 0;
+  if (launch_kernel(pl.v->wgrad_kernel, pl.grid, pl.threads, pl.smem, stream, args)) return 1;
+  return launch_reduce(dw, sc, g.c, sh->r * sh->s, pl.n_parts, stream);
 }
 
 // ---------------------------------------------------------------- host-buffer variants
@@ -463,6 +495,21 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy, const spio_g
                           const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes,
                           void* stream) {
   return launch_wgrad(dw, x, dy, shape, tune, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+int spio_conv2d_gw8_backward(void* dx, float* dw, const void* x, const void* dy, const void* w,
+                             const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
+                             const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes, void* stream,
+                             void* dw_ready) {
+  if (dx == nullptr && dw == nullptr) return fail("neither gradient was asked for");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dw != nullptr && launch_wgrad(dw, x, dy, shape, wgrad_tune, scratch, scratch_bytes, st)) return 1;
+  if (dw != nullptr && dw_ready != nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
+  // dgrad reads dy and w and writes dx; the weight-gradient kernels read x and dy and write
+  // scratch and dw.  Neither touches what the other writes, so dgrad need not wait for them.
+  if (dx != nullptr && launch_fwd(SPIO_GW8_DGRAD, dx, dy, w, nullptr, shape, dgrad_tune, st, dw != nullptr))
+    return 1;
+  return 0;
 }
 
 int spio_conv2d_gw8_wgrad_static(float* dw, const void* x, const void* dy,
@@ -621,11 +668,7 @@ int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const 
 int spio_conv2d_gw8_wgrad_reduce(float* dw, const float* scratch, int c, int taps, int n_parts, void* stream) {
   if (dw == nullptr || scratch == nullptr || c <= 0 || c % 8 || taps <= 0 || n_parts <= 0)
     return fail("bad argument");
-  const int total_f4 = c * taps * 2;
-  conv2d_gw8_wgrad_reduce_kernel<256><<<cdiv(total_f4, 8), 256, 0, (cudaStream_t)stream>>>(dw, scratch, c, taps,
-                                                                                           n_parts);
-  GW8_CUDA(cudaGetLastError());
-  return 0;
+  return launch_reduce(dw, scratch, c, taps, n_parts, (cudaStream_t)stream);
 }
 
 int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,

@@ -53,6 +53,9 @@ struct Gw8Geom {
   int n_split;         // wgrad: CTAs that share one chunk
   int warp_parts;      // wgrad: 1 = every compute warp writes its own partial (CTAs that walk
                        // several chunks), 0 = the warps of a group are summed inside the CTA
+  int independent;     // 1: the caller guarantees that this launch neither reads nor overwrites
+                       // anything the preceding kernels of its programmatic-launch chain write or
+                       // read, so the kernel does not wait for them
   // byte sizes derived from the above (kept here so that the kernels read them from the
   // constant bank instead of holding them in registers); pps = row pairs per slot
   unsigned in_pair_bytes;    // 2 rows of one image of the streamed operand: 2*bw*128

@@ -39,6 +39,22 @@ __device__ __forceinline__ u32 opaque_add(u32 a, u32 b) {
   return r;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+
+// When a kernel is launched with the programmatic-stream-serialization attribute its CTAs
+// may become resident while the preceding kernel of the stream is still running; this wait
+// returns once that kernel (and everything before it) has completed and its writes are
+// visible.  Without the attribute it returns at once.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Allows the next kernel of the stream, if it was launched with that attribute, to start
+// taking the SMs this grid's CTAs free as they exit.
+__device__ __forceinline__ void grid_dependency_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbar_init(u32 bar, u32 count) {

@@ -63,3 +63,20 @@ def wgrad(x, dy, sh, tune=None, scratch=None):
 
 def status():
     return _clib.device_status()
+
+
+def backward(x, dy, w, sh, dgrad_tune=None, wgrad_tune=None):
+    """(dx, dw) through the combined entry point."""
+    lib = _clib.load()
+    dx = torch.full((sh.n, sh.c, sh.h, sh.w), DEAD_VALUE, dtype=torch.float16, device=x.device)
+    dx = dx.contiguous(memory_format=CL)
+    dw = torch.full((sh.c, 8, sh.r, sh.s), DEAD_VALUE, dtype=torch.float32, device=x.device)
+    dw = dw.contiguous(memory_format=CL)
+    s = cshape(sh)
+    nbytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(ctypes.byref(s), _clib.tune_ref(wgrad_tune))
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    _clib.check(lib.spio_conv2d_gw8_backward(
+        dx.data_ptr(), dw.data_ptr(), x.data_ptr(), dy.data_ptr(), w.data_ptr(), ctypes.byref(s),
+        _clib.tune_ref(dgrad_tune), _clib.tune_ref(wgrad_tune), scratch.data_ptr(), nbytes,
+        torch.cuda.current_stream().cuda_stream, None))
+    return dx, dw

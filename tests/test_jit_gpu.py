@@ -134,7 +134,7 @@ def test_functional_path_with_jit_flag():
     token = flags.jit.set(True)
     try:
         xd.requires_grad_(True), wd.requires_grad_(True)
-        y = conv2d_gw8(xd, wd, bd, padding_y=1, padding_x=1)
+        y = conv2d_gw8(xd, wd, bd, padding_y=1, padding_x=1, groups=sh.c // 8)
         y.backward(dyd)
         kinds = [type(k) for c in caches for k in c._cache.values()]
         assert kinds and all(k is JitKernel for k in kinds)
