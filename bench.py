@@ -197,7 +197,7 @@ def run_ours(args) -> None:
     def backward():
         # wgrad -> reduce -> (dw_ready) -> dgrad, chained with programmatic dependent launch
         _clib.check(lib.spio_conv2d_gw8_backward(
-            dx.data_ptr(), dw.data_ptr(), x.data_ptr(), dy.data_ptr(), w.data_ptr(), shp, dgrad_tp, None,
+            dx.data_ptr(), dw.data_ptr(), None, x.data_ptr(), dy.data_ptr(), w.data_ptr(), shp, dgrad_tp, None,
             scratch.data_ptr(), scratch_bytes, sp, dw_ready.cuda_event if comm is not None else None))
 
     def step(events=None):

@@ -86,7 +86,12 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy,
                           const spio_gw8_shape* shape, const spio_gw8_tune* tune,
                           void* scratch, size_t scratch_bytes, void* stream);
 
-/* Both gradients of one layer in one call (dx or dw may be NULL to skip it).  Launches the
+/* All gradients of one layer in one call (dx or dw may be NULL to skip it).  dbias, if not
+ * NULL, receives the gradient of the bias, sum over n, h, w of dy (fp32, c values, 16-byte
+ * aligned): for filters with an odd number of taps the weight-gradient kernel computes it in
+ * the unused half of its last MMA, which replaces the separate reduction over dy of the
+ * reference (spio/functional/conv2d_gw8_function.py:136); for an even number of taps dbias
+ * must be NULL.  Launches the
  * weight-gradient kernel, its reduce kernel and the input-gradient kernel back to back with
  * programmatic dependent launch: the input-gradient kernel shares no output with the other
  * two, so its CTAs take over SMs as theirs finish instead of waiting for the whole grid to
@@ -94,7 +99,7 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy,
  * point, so a data-parallel caller can make its communication stream wait for the event and
  * all-reduce dw while the input gradient is still being computed.  Replaces the two launches of the reference's
  * backward operator (spio/functional/conv2d_gw8_function.py:93-147). */
-int spio_conv2d_gw8_backward(void* dx, float* dw, const void* x, const void* dy, const void* w,
+int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, const void* dy, const void* w,
                              const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
                              const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes,
                              void* stream, void* dw_ready);
@@ -168,7 +173,7 @@ int spio_function_launch(void* function, int grid, int block, int smem_bytes, vo
  * parameter lists:
  *   fprop / dgrad: (in_map, out_map, geom, const half* w, const float* bias, int ns, int nob, int* status)
  *   wgrad:         (in_map, out_map, geom, float* scratch, int ns, int* status), followed by
- *                  spio_conv2d_gw8_wgrad_reduce(dw, scratch, c, r*s, n_parts, stream). */
+ *                  spio_conv2d_gw8_wgrad_reduce(dw, dbias or NULL, scratch, c, r*s, n_parts, stream). */
 typedef struct spio_gw8_launch {
   unsigned long long in_map[16];   /* CUtensorMap of the streamed operand (x; dy for dgrad) */
   unsigned long long out_map[16];  /* CUtensorMap of the tiled operand (y; dx; dy for wgrad) */
@@ -183,7 +188,8 @@ int spio_conv2d_gw8_plan_jit(int kind, const spio_gw8_shape* shape, const spio_g
                              int smem_optin_bytes, spio_gw8_plan_info* info);
 int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
                                    const void* streamed, const void* tiled, spio_gw8_launch* out);
-int spio_conv2d_gw8_wgrad_reduce(float* dw, const float* scratch, int c, int taps, int n_parts, void* stream);
+int spio_conv2d_gw8_wgrad_reduce(float* dw, float* dbias, const float* scratch, int c, int taps, int n_parts,
+                                 void* stream);
 
 /* Number of compiled (r, s, wpg, tpw, pps) variants, and the i-th one. */
 int spio_conv2d_gw8_num_variants(void);

@@ -71,7 +71,7 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p, c_size_t, c_void_p]),
     "spio_conv2d_gw8_backward": (
         c_int,
-        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), POINTER(Tune),
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), POINTER(Tune),
          c_void_p, c_size_t, c_void_p, c_void_p]),
     "spio_conv2d_gw8_wgrad_static": (
         c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
@@ -101,7 +101,7 @@ SIGNATURES = {
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),
     "spio_conv2d_gw8_prepare_launch": (
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_void_p, c_void_p, POINTER(Launch)]),
-    "spio_conv2d_gw8_wgrad_reduce": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "spio_conv2d_gw8_wgrad_reduce": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "spio_conv2d_gw8_num_variants": (c_int, []),
     "spio_conv2d_gw8_variant": (
         c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),

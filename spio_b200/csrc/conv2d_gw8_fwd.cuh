@@ -101,6 +101,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
       // ---------------------------------------------------------- load warp
       if (lane == 0) {
         prefetch_tensormap(&in_map);
+        const u64 in_policy = make_l2_policy(g.hint_in);
         Gw8Walk walk(u0, u1, g);
         Gw8Segment seg;
         int slot = 0;
@@ -123,7 +124,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
             desc[slot].flags = 0;
             mbar_arrive_expect_tx(full(slot), g.slot_bytes);
             tma_load_4d(ring + (u32)slot * g.slot_bytes, &in_map, full(slot), c0, w0,
-                        2 * (seg.m0 + PPS * i) - g.pad_h, n0);
+                        2 * (seg.m0 + PPS * i) - g.pad_h, n0, g.hint_in, in_policy);
             if (++slot == ns) {
               slot = 0;
               par ^= 1u;

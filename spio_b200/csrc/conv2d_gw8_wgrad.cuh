@@ -23,10 +23,16 @@
 
 namespace spio_b200 {
 
-// Scratch layout: [chunk][part][64 local out-channels][taps][8 in-channels] fp32 with
-// part = split index of the CTA, n_parts = n_split: the WPG warps of a group are summed
+// Scratch layout: [chunk][part]{[64 local out-channels][taps][8 in-channels], [64 bias sums]} fp32
+// with part = split index of the CTA, n_parts = n_split: the WPG warps of a group are summed
 // inside the CTA through shared memory before the partial is written.  CTAs that walk
 // several chunks (more chunks than CTAs) keep one part per warp instead, n_parts = n_split * WPG.
+//
+// Bias gradient for free: two filter taps share one m16n8k16 (tap 2i in rows 0-7 of A, tap
+// 2i+1 in rows 8-15).  With an odd number of taps the last MMA has rows 8-15 to spare; they
+// are fed ones, so rows 8-15 of its accumulator hold sum over pixels of dy[pixel][k], which
+// is the gradient of the bias.  It is written behind the weight partial of each part.
+#define GW8_PART_FLOATS(taps) (64 * (taps) * 8 + 64)
 // The kernel body is a device function so that both the ahead-of-time instantiations and
 // the just-in-time wrappers (one extern "C" kernel per layer shape) can share it.
 template <class Cfg>
@@ -37,6 +43,8 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
   constexpr int E = Cfg::E, WIN = Cfg::WIN, NT = Cfg::NT, NCW = Cfg::NCW;
   constexpr int NPH = WIN / 2;
   constexpr int NACC = (NT + 1) / 2;
+  constexpr bool BIAS = (NT & 1) != 0;    // the spare half of the last MMA sums dy
+  constexpr u32 ONES = 0x3C003C00u;       // half2(1, 1)
   constexpr int MAX_NS = 16;
 
   extern __shared__ unsigned char smem_raw[];
@@ -90,6 +98,8 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     if (lane == 0) {
       prefetch_tensormap(&x_map);
       prefetch_tensormap(&dy_map);
+      const u64 x_policy = make_l2_policy(g.hint_in);
+      const u64 dy_policy = make_l2_policy(g.hint_tiled);
       int slot = 0;
       u32 par = 0;
       bool ok = true;
@@ -109,10 +119,10 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
             const bool with_dy = stage_has_pairs(i);
             mbar_arrive_expect_tx(full(slot), with_dy ? stage_bytes : xslot_bytes);
             tma_load_4d(dst, &x_map, full(slot), c0, seg.ct * g.wt - g.pad_w,
-                        2 * (seg.m0 + PPS * i) - g.pad_h, n0);
+                        2 * (seg.m0 + PPS * i) - g.pad_h, n0, g.hint_in, x_policy);
             if (with_dy)
               tma_load_4d(dst + xslot_bytes, &dy_map, full(slot), c0, seg.ct * g.wt,
-                          2 * (seg.m0 + PPS * i - E), n0);
+                          2 * (seg.m0 + PPS * i - E), n0, g.hint_tiled, dy_policy);
             if (++slot == ns) {
               slot = 0;
               par ^= 1u;
@@ -226,7 +236,7 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
                         mma_m16n8k16(acc[k], X[t][pa0][sa], X[t][pb0][sb], X[t][pa1][sa],
                                      X[t][pb1][sb], d0, d1);
                       } else {
-                        mma_m16n8k16(acc[k], X[t][pa0][sa], 0u, X[t][pa1][sa], 0u, d0, d1);
+                        mma_m16n8k16(acc[k], X[t][pa0][sa], ONES, X[t][pa1][sa], ONES, d0, d1);
                       }
                     }
                   }
@@ -281,7 +291,8 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
         asm volatile("bar.sync 1, %0;" ::"r"(NCW * 32) : "memory");  // red may be reused
       }
       if (wsub == 0 || !cta_sum) {
-        float* part = scratch + ((size_t)ck * n_parts + (size_t)(cta_sum ? si : si * WPG + wsub)) * (64 * NT * 8);
+        float* part = scratch + ((size_t)ck * n_parts + (size_t)(cta_sum ? si : si * WPG + wsub)) *
+                                    GW8_PART_FLOATS(NT);
         const int kl = grp * 8 + 2 * t4;
 #pragma unroll
         for (int i = 0; i < NACC; ++i) {
@@ -292,6 +303,10 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
             part[((kl + 0) * NT + fb) * 8 + gq] = acc[i][2];
             part[((kl + 1) * NT + fb) * 8 + gq] = acc[i][3];
           }
+        }
+        if (BIAS && gq == 0) {  // rows 8-15 of the last accumulator are eight copies of the sum
+          part[64 * NT * 8 + kl + 0] = acc[NACC - 1][2];
+          part[64 * NT * 8 + kl + 1] = acc[NACC - 1][3];
         }
       }
     }
@@ -312,15 +327,16 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
   conv2d_gw8_wgrad_body<Cfg>(x_map, dy_map, g, scratch, ns, status);
 }
 
-// dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], added in a
-// fixed order.  A block of 256 threads owns 8 float4 columns of dw; thread (cx, q) adds
-// the parts q, q+32, ... of column cx, then the 32 partial sums of a column are combined
-// by two shuffle steps and a pass over shared memory.  Launch with 256 threads and
-// grid = ceil(c * taps * 2 / 8).
+// dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], and, when dbias
+// is not NULL, dbias[k] = sum over parts of the bias sums behind it, added in a fixed order.
+// A block of 256 threads owns 8 float4 columns of a part; thread (cx, q) adds the parts q,
+// q+32, ... of column cx, then the 32 partial sums of a column are combined by two shuffle
+// steps and a pass over shared memory.  Launch with 256 threads and
+// grid = ceil(n_chunks * GW8_PART_FLOATS(taps) / 4 / 8).
 template <int THREADS = 256>
 __global__ void __launch_bounds__(THREADS)
-conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__ scratch, int c,
-                               int taps, int n_parts) {
+conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, float* __restrict__ dbias,
+                               const float* __restrict__ scratch, int c, int taps, int n_parts) {
   __shared__ float4 red[8][8];
   // Let an independent successor take SMs as they become free, then wait for the partials.
   grid_dependency_launch_dependents();
@@ -329,13 +345,23 @@ conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__
   const int pl = (threadIdx.x >> 3) & 3;
   const int wy = threadIdx.x >> 5;
   const int q = wy * 4 + pl;
-  const int chunk_f4 = 64 * taps * 8 / 4;  // float4 per chunk
-  const int total_f4 = c * taps * 8 / 4;   // float4 in dw
+  const int dw_f4 = 64 * taps * 2;                 // float4 of weight gradient per chunk
+  const int chunk_f4 = GW8_PART_FLOATS(taps) / 4;  // float4 per part
+  const int n_chunks = (c + 63) / 64;
   const int col = blockIdx.x * 8 + cx;
+  const int ck = col / chunk_f4;
+  const int e = col - ck * chunk_f4;
+  // where the column goes: a float4 of dw, a float4 of dbias, or nowhere (channels >= c)
+  float4* out = nullptr;
+  if (ck < n_chunks) {
+    if (e < dw_f4) {
+      if (ck * 64 + e / (taps * 2) < c) out = reinterpret_cast<float4*>(dw) + (size_t)ck * dw_f4 + e;
+    } else if (dbias != nullptr && ck * 64 + 4 * (e - dw_f4) < c) {
+      out = reinterpret_cast<float4*>(dbias) + ck * 16 + (e - dw_f4);
+    }
+  }
   float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (col < total_f4) {
-    const int ck = col / chunk_f4;
-    const int e = col - ck * chunk_f4;
+  if (out != nullptr) {
     const float4* src =
         reinterpret_cast<const float4*>(scratch) + (size_t)ck * n_parts * chunk_f4 + e;
 #pragma unroll 4
@@ -356,7 +382,7 @@ conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__
   }
   if (pl == 0) red[wy][cx] = sum;
   __syncthreads();
-  if (wy == 0 && pl == 0 && col < total_f4) {
+  if (wy == 0 && pl == 0 && out != nullptr) {
 #pragma unroll
     for (int w = 1; w < 8; ++w) {
       const float4 v = red[w][cx];
@@ -365,7 +391,7 @@ conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, const float* __restrict__
       sum.z += v.z;
       sum.w += v.w;
     }
-    reinterpret_cast<float4*>(dw)[col] = sum;
+    *out = sum;
   }
 }
 

@@ -297,7 +297,7 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
     const int red_need = (v->wpg - 1) * 8 * ((sh->r * sh->s + 1) / 2) * 4 * 32 * (int)sizeof(float);
     if (red_need > pl.smem - kAlignSlack) g.warp_parts = 1;  // staging would not fit in the ring
     pl.n_parts = g.n_split * (g.warp_parts ? v->wpg : 1);
-    pl.scratch_bytes = (size_t)g.n_chunks * pl.n_parts * 64 * sh->r * sh->s * 8 * sizeof(float);
+    pl.scratch_bytes = (size_t)g.n_chunks * pl.n_parts * GW8_PART_FLOATS(sh->r * sh->s) * sizeof(float);
   } else {
     pl.threads = v->fwd_threads;
     pl.grid = (int)(total < ctas ? total : ctas);
@@ -339,6 +339,15 @@ bool pdl_enabled() {
   return on;
 }
 
+// SPIO_L2_HINTS=0 turns the L2 eviction hints of the combined backward call off.
+bool l2_hints_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SPIO_L2_HINTS");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
 // Launches with the programmatic-stream-serialization attribute: the kernel's CTAs may take
 // SMs while the preceding kernel of the stream drains, and the kernel itself waits
 // (griddepcontrol.wait) before it touches global memory.
@@ -359,13 +368,14 @@ int launch_kernel(const void* func, int grid, int threads, size_t smem, cudaStre
 
 int launch_fwd(int kind, void* out, const void* in, const void* w, const float* bias,
                const spio_gw8_shape* sh, const spio_gw8_tune* tune, cudaStream_t stream,
-               bool independent = false) {
+               bool independent = false, int hint_in = L2_HINT_NONE) {
   if (out == nullptr || in == nullptr || w == nullptr) return fail("NULL tensor pointer");
   const DeviceInfo* d = nullptr;
   if (device_info(&d)) return 1;
   Plan pl;
   if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
   pl.g.independent = (independent && pdl_enabled()) ? 1 : 0;
+  pl.g.hint_in = hint_in;
   const Gw8Geom& g = pl.g;
   CUtensorMap in_map, out_map;
   if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
@@ -378,16 +388,21 @@ int launch_fwd(int kind, void* out, const void* in, const void* w, const float* 
   return launch_kernel(pl.v->fwd_kernel, pl.grid, pl.threads, pl.smem, stream, args);
 }
 
-int launch_reduce(float* dw, const float* scratch, int c, int taps, int n_parts, cudaStream_t stream) {
-  const int total_f4 = c * taps * 2;
-  void* args[] = {&dw, &scratch, &c, &taps, &n_parts};
+int launch_reduce(float* dw, float* dbias, const float* scratch, int c, int taps, int n_parts,
+                  cudaStream_t stream) {
+  if (dbias != nullptr && taps % 2 == 0)
+    return fail("the fused bias gradient needs an odd number of filter taps (r * s)");
+  if ((reinterpret_cast<size_t>(dbias) & 15u) != 0) return fail("dbias must be 16-byte aligned");
+  const int total_f4 = cdiv(c, 64) * (GW8_PART_FLOATS(taps) / 4);
+  void* args[] = {&dw, &dbias, &scratch, &c, &taps, &n_parts};
   return launch_kernel(reinterpret_cast<const void*>(&conv2d_gw8_wgrad_reduce_kernel<256>), cdiv(total_f4, 8), 256,
                        0, stream, args);
 }
 
 int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape* sh,
                  const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, int hint_x = L2_HINT_NONE, int hint_dy = L2_HINT_NONE,
+                 float* dbias = nullptr) {
   if (dw == nullptr || x == nullptr || dy == nullptr) return fail("NULL tensor pointer");
   const DeviceInfo* d = nullptr;
   if (device_info(&d)) return 1;
@@ -396,6 +411,8 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
   if (scratch == nullptr || scratch_bytes < pl.scratch_bytes) return fail("wgrad scratch buffer is too small");
   if ((reinterpret_cast<size_t>(scratch) & 15u) != 0 || (reinterpret_cast<size_t>(dw) & 15u) != 0)
     return fail("dw and scratch must be 16-byte aligned");
+  pl.g.hint_in = hint_x;
+  pl.g.hint_tiled = hint_dy;
   const Gw8Geom& g = pl.g;
   CUtensorMap x_map, dy_map;
   if (encode_map(&x_map, x, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
@@ -405,7 +422,7 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
   int* status = d->status;
   void* args[] = {&x_map, &dy_map, (void*)&g, &sc, &ns, &status};
   if (launch_kernel(pl.v->wgrad_kernel, pl.grid, pl.threads, pl.smem, stream, args)) return 1;
-  return launch_reduce(dw, sc, g.c, sh->r * sh->s, pl.n_parts, stream);
+  return launch_reduce(dw, dbias, sc, g.c, sh->r * sh->s, pl.n_parts, stream);
 }
 
 // ---------------------------------------------------------------- host-buffer variants
@@ -497,17 +514,28 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy, const spio_g
   return launch_wgrad(dw, x, dy, shape, tune, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
-int spio_conv2d_gw8_backward(void* dx, float* dw, const void* x, const void* dy, const void* w,
+int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, const void* dy, const void* w,
                              const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
                              const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes, void* stream,
                              void* dw_ready) {
   if (dx == nullptr && dw == nullptr) return fail("neither gradient was asked for");
+  if (dbias != nullptr && dw == nullptr) return fail("the bias gradient is computed together with dw");
+  if (dbias != nullptr && (shape == nullptr || (shape->r * shape->s) % 2 == 0))
+    return fail("the fused bias gradient needs an odd number of filter taps (r * s)");
   cudaStream_t st = (cudaStream_t)stream;
-  if (dw != nullptr && launch_wgrad(dw, x, dy, shape, wgrad_tune, scratch, scratch_bytes, st)) return 1;
+  // Both kernels read dy.  The weight-gradient kernel asks the L2 to keep dy and to let x go
+  // first, so that the input-gradient kernel finds as much of dy in the cache as fits; that
+  // kernel in turn marks dy as done with.
+  const bool both = dx != nullptr && dw != nullptr && l2_hints_enabled();
+  if (dw != nullptr && launch_wgrad(dw, x, dy, shape, wgrad_tune, scratch, scratch_bytes, st,
+                                    both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE,
+                                    both ? L2_HINT_EVICT_LAST : L2_HINT_NONE, dbias))
+    return 1;
   if (dw != nullptr && dw_ready != nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
   // dgrad reads dy and w and writes dx; the weight-gradient kernels read x and dy and write
   // scratch and dw.  Neither touches what the other writes, so dgrad need not wait for them.
-  if (dx != nullptr && launch_fwd(SPIO_GW8_DGRAD, dx, dy, w, nullptr, shape, dgrad_tune, st, dw != nullptr))
+  if (dx != nullptr && launch_fwd(SPIO_GW8_DGRAD, dx, dy, w, nullptr, shape, dgrad_tune, st, dw != nullptr,
+                                  both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE))
     return 1;
   return 0;
 }
@@ -665,10 +693,11 @@ int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const 
   return 0;
 }
 
-int spio_conv2d_gw8_wgrad_reduce(float* dw, const float* scratch, int c, int taps, int n_parts, void* stream) {
+int spio_conv2d_gw8_wgrad_reduce(float* dw, float* dbias, const float* scratch, int c, int taps, int n_parts,
+                                 void* stream) {
   if (dw == nullptr || scratch == nullptr || c <= 0 || c % 8 || taps <= 0 || n_parts <= 0)
     return fail("bad argument");
-  return launch_reduce(dw, scratch, c, taps, n_parts, (cudaStream_t)stream);
+  return launch_reduce(dw, dbias, scratch, c, taps, n_parts, (cudaStream_t)stream);
 }
 
 int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,

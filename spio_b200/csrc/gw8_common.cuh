@@ -56,6 +56,8 @@ struct Gw8Geom {
   int independent;     // 1: the caller guarantees that this launch neither reads nor overwrites
                        // anything the preceding kernels of its programmatic-launch chain write or
                        // read, so the kernel does not wait for them
+  int hint_in;         // L2 eviction hint (L2_HINT_*) for loads of the streamed operand
+  int hint_tiled;      // wgrad: the same for loads of dy
   // byte sizes derived from the above (kept here so that the kernels read them from the
   // constant bank instead of holding them in registers); pps = row pairs per slot
   unsigned in_pair_bytes;    // 2 rows of one image of the streamed operand: 2*bw*128

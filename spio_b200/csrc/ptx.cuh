@@ -144,6 +144,38 @@ __device__ __forceinline__ void tma_load_4d(u32 dst, const void* tmap, u32 bar, 
       : "memory");
 }
 
+// L2 eviction-priority policies for loads: 0 = none, 1 = evict first (data that is not read
+// again soon), 2 = evict last (data the next kernel reads again).
+enum { L2_HINT_NONE = 0, L2_HINT_EVICT_FIRST = 1, L2_HINT_EVICT_LAST = 2 };
+
+__device__ __forceinline__ u64 make_l2_policy(int hint) {
+  u64 p = 0;
+  if (hint == L2_HINT_EVICT_FIRST)
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  else if (hint == L2_HINT_EVICT_LAST)
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// tma_load_4d with an L2 cache policy made by make_l2_policy (hint != L2_HINT_NONE).
+__device__ __forceinline__ void tma_load_4d_hint(u32 dst, const void* tmap, u32 bar, int c0, int c1,
+                                                 int c2, int c3, u64 policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+      : "memory");
+}
+
+// Either form, chosen by the hint the policy was made from.
+__device__ __forceinline__ void tma_load_4d(u32 dst, const void* tmap, u32 bar, int c0, int c1, int c2,
+                                            int c3, int hint, u64 policy) {
+  if (hint == L2_HINT_NONE)
+    tma_load_4d(dst, tmap, bar, c0, c1, c2, c3);
+  else
+    tma_load_4d_hint(dst, tmap, bar, c0, c1, c2, c3, policy);
+}
+
 // Tiled store of one box; elements outside the tensor are dropped.  All coordinates
 // must be non-negative.
 __device__ __forceinline__ void tma_store_4d(const void* tmap, u32 src, int c0, int c1, int c2,

@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..kernels import Conv2dGw8Params, conv2d_gw8_kernel_factory, conv2d_gw8_wgrad_kernel_factory
-from ..kernels.kernel import launch_backward
+from ..kernels.kernel import Kernel, launch_backward
 from ..util.tensor_format import to_channels_last
 
 
@@ -95,11 +95,8 @@ def conv2d_gw8_backward_op(
     grad_output, inputs, weight = to_channels_last(grad_output, inputs, weight)
     params = Conv2dGw8Params.from_tensors(inputs, weight, bias, padding=(padding_y, padding_x))
 
-    grad_bias = _absent(inputs, torch.float32)
-    if needs_bias_grad:
-        grad_bias = grad_output.sum(dim=(0, 2, 3), dtype=torch.float32)
-
     grad_weight = _absent(inputs, torch.float32)
+    wgrad_kernel = dgrad_kernel = None
     if needs_weight_grad:
         # The kernel overwrites grad_weight, so no zero fill is needed.
         grad_weight = torch.empty(params.weight_shape, device=inputs.device, dtype=torch.float32,
@@ -110,11 +107,19 @@ def conv2d_gw8_backward_op(
         grad_input = torch.empty_like(inputs)
         dgrad_kernel = conv2d_gw8_kernel_factory.get_kernel(params, inputs.device, igrad=True)
 
-    if needs_weight_grad and needs_input_grad:
+    # With an odd number of filter taps the weight-gradient kernel sums grad_output over
+    # n, h, w in the unused half of its last MMA; otherwise torch does that reduction.
+    grad_bias = _absent(inputs, torch.float32)
+    fused_bias = (needs_bias_grad and needs_weight_grad and (params.r * params.s) % 2 == 1
+                  and type(wgrad_kernel) is Kernel)
+    if needs_bias_grad:
+        grad_bias = (torch.empty(params.k, device=inputs.device, dtype=torch.float32) if fused_bias
+                     else grad_output.sum(dim=(0, 2, 3), dtype=torch.float32))
+
+    if needs_weight_grad:
         # one call: the input-gradient kernel starts on SMs as the weight-gradient kernels free them
-        launch_backward(wgrad_kernel, dgrad_kernel, grad_input, grad_weight, inputs, grad_output, weight)
-    elif needs_weight_grad:
-        wgrad_kernel(grad_weight, inputs, grad_output)
+        launch_backward(wgrad_kernel, dgrad_kernel, grad_input, grad_weight, inputs, grad_output, weight,
+                        grad_bias if fused_bias else None)
     elif needs_input_grad:
         dgrad_kernel(grad_input, grad_output, weight, None)
     return grad_input, grad_weight, grad_bias

@@ -133,7 +133,7 @@ class JitKernel(Kernel):
                 self.function.launch(lp.grid, lp.threads, kargs, shared_mem_bytes=lp.smem_bytes, stream=stream)
                 if self.kind == _clib.WGRAD:
                     _clib.check(self._lib.spio_conv2d_gw8_wgrad_reduce(
-                        args[0].data_ptr(), scratch.data_ptr(), self.params.c, self.params.r * self.params.s,
+                        args[0].data_ptr(), None, scratch.data_ptr(), self.params.c, self.params.r * self.params.s,
                         lp.n_parts, stream))
         except Exception as exc:
             raise ValueError(f"Error in kernel {self}: {exc}") from exc

@@ -124,28 +124,35 @@ class Kernel:
         return f"{self.kernel_name} {self.config}"
 
 
-def launch_backward(wgrad_kernel: Kernel, dgrad_kernel: Kernel, grad_input, grad_weight, inputs,
-                    grad_output, weight) -> None:
-    """Both gradients of a layer.  Two ahead-of-time kernels go through the library's combined
+def launch_backward(wgrad_kernel: Kernel, dgrad_kernel: Optional[Kernel], grad_input, grad_weight, inputs,
+                    grad_output, weight, grad_bias=None) -> None:
+    """Weight gradient, optionally the bias gradient (odd number of filter taps only) and,
+    with ``dgrad_kernel``, the input gradient of a layer.  Two ahead-of-time kernels go through the library's combined
     entry point, which chains weight gradient, reduce and input gradient with programmatic
     dependent launch; anything else (a just-in-time kernel) is launched one after the other."""
-    if type(wgrad_kernel) is not Kernel or type(dgrad_kernel) is not Kernel:
+    if type(wgrad_kernel) is not Kernel or (dgrad_kernel is not None and type(dgrad_kernel) is not Kernel):
+        if grad_bias is not None:
+            raise ValueError("the fused bias gradient needs the built-in weight-gradient kernel")
         wgrad_kernel(grad_weight, inputs, grad_output)
-        dgrad_kernel(grad_input, grad_output, weight, None)
+        if dgrad_kernel is not None:
+            dgrad_kernel(grad_input, grad_output, weight, None)
         return
-    if wgrad_kernel._lib is None or dgrad_kernel._lib is None:
+    if wgrad_kernel._lib is None or (dgrad_kernel is not None and dgrad_kernel._lib is None):
         raise ValueError(f"Error in kernel {wgrad_kernel}: kernel is not loaded")
     try:
         wgrad_kernel._args_checker((grad_weight, inputs, grad_output))
-        dgrad_kernel._args_checker((grad_input, grad_output, weight, None))
+        if dgrad_kernel is not None:
+            dgrad_kernel._args_checker((grad_input, grad_output, weight, None))
         dev = inputs.device
         stream = torch.cuda.current_stream(dev).cuda_stream
         nbytes = wgrad_kernel._scratch_bytes
         with torch.cuda.device(dev):
             scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
             rc = wgrad_kernel._lib.spio_conv2d_gw8_backward(
-                grad_input.data_ptr(), grad_weight.data_ptr(), inputs.data_ptr(), grad_output.data_ptr(),
-                weight.data_ptr(), ctypes.byref(wgrad_kernel._shape), dgrad_kernel._tune_ref(),
+                grad_input.data_ptr() if dgrad_kernel is not None else None, grad_weight.data_ptr(),
+                grad_bias.data_ptr() if grad_bias is not None else None, inputs.data_ptr(),
+                grad_output.data_ptr(), weight.data_ptr(), ctypes.byref(wgrad_kernel._shape),
+                dgrad_kernel._tune_ref() if dgrad_kernel is not None else None,
                 wgrad_kernel._tune_ref(), scratch.data_ptr(), nbytes, stream, None)
         _clib.check(rc)
     except Exception as exc:

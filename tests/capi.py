@@ -65,8 +65,8 @@ def status():
     return _clib.device_status()
 
 
-def backward(x, dy, w, sh, dgrad_tune=None, wgrad_tune=None):
-    """(dx, dw) through the combined entry point."""
+def backward(x, dy, w, sh, dgrad_tune=None, wgrad_tune=None, with_bias=False):
+    """(dx, dw) or (dx, dw, dbias) through the combined entry point."""
     lib = _clib.load()
     dx = torch.full((sh.n, sh.c, sh.h, sh.w), DEAD_VALUE, dtype=torch.float16, device=x.device)
     dx = dx.contiguous(memory_format=CL)
@@ -75,8 +75,9 @@ def backward(x, dy, w, sh, dgrad_tune=None, wgrad_tune=None):
     s = cshape(sh)
     nbytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(ctypes.byref(s), _clib.tune_ref(wgrad_tune))
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=x.device)
+    db = torch.full((sh.c,), DEAD_VALUE, dtype=torch.float32, device=x.device) if with_bias else None
     _clib.check(lib.spio_conv2d_gw8_backward(
-        dx.data_ptr(), dw.data_ptr(), x.data_ptr(), dy.data_ptr(), w.data_ptr(), ctypes.byref(s),
-        _clib.tune_ref(dgrad_tune), _clib.tune_ref(wgrad_tune), scratch.data_ptr(), nbytes,
-        torch.cuda.current_stream().cuda_stream, None))
-    return dx, dw
+        dx.data_ptr(), dw.data_ptr(), db.data_ptr() if with_bias else None, x.data_ptr(), dy.data_ptr(),
+        w.data_ptr(), ctypes.byref(s), _clib.tune_ref(dgrad_tune), _clib.tune_ref(wgrad_tune),
+        scratch.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream, None))
+    return (dx, dw, db) if with_bias else (dx, dw)

@@ -61,10 +61,49 @@ def test_backward_single_gradient_and_errors():
     s = capi.cshape(sh)
     dx = torch.empty_like(xd)
     st = torch.cuda.current_stream().cuda_stream
-    assert lib.spio_conv2d_gw8_backward(dx.data_ptr(), None, xd.data_ptr(), dyd.data_ptr(), wd.data_ptr(),
+    assert lib.spio_conv2d_gw8_backward(dx.data_ptr(), None, None, xd.data_ptr(), dyd.data_ptr(), wd.data_ptr(),
                                         ctypes.byref(s), None, None, None, 0, st, None) == 0
     assert torch.equal(dx, capi.dgrad(dyd, wd, sh))
-    assert lib.spio_conv2d_gw8_backward(None, None, xd.data_ptr(), dyd.data_ptr(), wd.data_ptr(),
+    assert lib.spio_conv2d_gw8_backward(None, None, None, xd.data_ptr(), dyd.data_ptr(), wd.data_ptr(),
                                         ctypes.byref(s), None, None, None, 0, st, None) != 0
     assert b"neither" in lib.spio_b200_last_error()
     assert capi.status() == 0
+
+
+ODD_TAP_CASES = [case for case in REFERENCE_TEST_SHAPES if (case[0].r * case[0].s) % 2 == 1][::4]
+
+
+@pytest.mark.parametrize("case", ODD_TAP_CASES, ids=ident)
+def test_fused_bias_gradient(case):
+    """dbias from the spare half of the weight-gradient MMA equals the fp64 sum of dy over
+    n, h, w (dy is fp16, the kernel adds in fp32)."""
+    sh, _ = case
+    x, w, _, dy = O.make_inputs(sh, seed=33, bias=False)
+    xd, wd, dyd = (capi.to_dev(t) for t in (x, w, dy))
+    dx, dw, db = capi.backward(xd, dyd, wd, sh, with_bias=True)
+    ref = dy.double().sum(dim=(0, 2, 3))
+    scale = float(dy.double().abs().sum(dim=(0, 2, 3)).max())
+    assert float((db.double().cpu() - ref).abs().max()) <= 1e-5 * scale + 1e-6
+    assert torch.equal(dw, capi.wgrad(xd, dyd, sh))   # the weight gradient is unchanged by it
+    assert torch.equal(dx, capi.dgrad(dyd, wd, sh))
+    assert capi.status() == 0
+
+
+def test_fused_bias_gradient_full_size_and_channel_tail():
+    for sh in (O.Shape(64, 64, 56, 56, 3, 3, 1, 1), O.Shape(9, 200, 14, 14, 3, 3, 1, 1),
+               O.Shape(5, 72, 9, 31, 5, 5, 2, 2), O.Shape(7, 136, 12, 12, 1, 1, 0, 0)):
+        x, w, _, dy = O.make_inputs(sh, seed=1, bias=False)
+        xd, wd, dyd = (capi.to_dev(t) for t in (x, w, dy))
+        _, _, db = capi.backward(xd, dyd, wd, sh, with_bias=True)
+        ref = dy.double().sum(dim=(0, 2, 3))
+        scale = float(dy.double().abs().sum(dim=(0, 2, 3)).max())
+        assert float((db.double().cpu() - ref).abs().max()) <= 1e-5 * scale + 1e-6, str(sh)
+    assert capi.status() == 0
+
+
+def test_fused_bias_gradient_rejects_even_taps():
+    sh = O.Shape(4, 64, 16, 16, 2, 2, 0, 0)
+    x, w, _, dy = O.make_inputs(sh, seed=2, bias=False)
+    xd, wd, dyd = (capi.to_dev(t) for t in (x, w, dy))
+    with pytest.raises(ValueError, match="odd number of filter taps"):
+        capi.backward(xd, dyd, wd, sh, with_bias=True)

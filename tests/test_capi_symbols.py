@@ -66,7 +66,7 @@ def test_planner_respects_limits(case, kind):
     assert p["n_image_groups"] * p["nb"] >= sh.n
     assert p["n_chunks"] * 64 >= sh.c
     if kind == _clib.WGRAD:
-        assert p["scratch_bytes"] in (p["n_chunks"] * p["n_split"] * k * 64 * sh.r * sh.s * 8 * 4 for k in (1, p["wpg"]))
+        assert p["scratch_bytes"] in (p["n_chunks"] * p["n_split"] * k * (64 * sh.r * sh.s * 8 + 64) * 4 for k in (1, p["wpg"]))
         assert p["grid"] == (p["n_split"] * p["n_chunks"] if p["n_chunks"] <= SMS else SMS)
     else:
         assert p["scratch_bytes"] == 0
