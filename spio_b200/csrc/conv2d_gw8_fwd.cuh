@@ -384,6 +384,10 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   }
 
   __syncthreads();
+  // A kernel that did not wait for its predecessors at the start must not COMPLETE before
+  // them either: a later kernel that waits for this one relies on that to be ordered after
+  // the whole chain.  By now they have long finished, so this returns at once.
+  if (g.independent) grid_dependency_wait();
   if (abort_flag) {
     // Let copies that may still be in flight land before the CTA gives up its
     // shared memory, then report.

@@ -313,6 +313,10 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
   }
 
   __syncthreads();
+  // A kernel that did not wait for its predecessors at the start must not COMPLETE before
+  // them either: a later kernel that waits for this one relies on that to be ordered after
+  // the whole chain.  By now they have long finished, so this returns at once.
+  if (g.independent) grid_dependency_wait();
   if (abort_flag) {
     for (int i = 0; i < 64; ++i) __nanosleep(20000);
     if (threadIdx.x == 0) atomicExch(status, (int)GW8_WAIT_TIMEOUT);
