@@ -43,6 +43,9 @@ typedef struct spio_gw8_tune {
   int nb;    /* images per ring slot */
   int grid;  /* CTAs; 0 = one per SM */
   int pps;   /* row pairs per ring slot: 1 or 2 */
+  int engine; /* 0 = the planner chooses; 1 = warp-level mma.sync kernels; 2 = tcgen05 kernel with the
+                 accumulators in tensor memory (fprop and dgrad, filters up to 3 x 3; it ignores
+                 wpg, tpw, nb and pps) */
 } spio_gw8_tune;
 
 /* What a launch will look like; filled by spio_conv2d_gw8_plan. */
@@ -50,6 +53,7 @@ typedef struct spio_gw8_plan_info {
   int wpg, tpw, ns, nob, ncb, nb, grid, threads;
   int pps, smem_bytes;
   int n_chunks, n_image_groups, n_col_tiles, n_pairs, n_split;
+  int engine;           /* 1 or 2, see spio_gw8_tune */
   size_t scratch_bytes; /* wgrad only */
 } spio_gw8_plan_info;
 

@@ -26,7 +26,7 @@ class Shape(Structure):
 class Tune(Structure):
     """struct spio_gw8_tune; zero fields are chosen by the library."""
 
-    _fields_ = [(k, c_int) for k in ("wpg", "tpw", "ns", "nob", "ncb", "nb", "grid", "pps")]
+    _fields_ = [(k, c_int) for k in ("wpg", "tpw", "ns", "nob", "ncb", "nb", "grid", "pps", "engine")]
 
 
 class PlanInfo(Structure):
@@ -36,7 +36,7 @@ class PlanInfo(Structure):
         (k, c_int)
         for k in (
             "wpg", "tpw", "ns", "nob", "ncb", "nb", "grid", "threads", "pps", "smem_bytes",
-            "n_chunks", "n_image_groups", "n_col_tiles", "n_pairs", "n_split",
+            "n_chunks", "n_image_groups", "n_col_tiles", "n_pairs", "n_split", "engine",
         )
     ] + [("scratch_bytes", c_size_t)]
 

@@ -44,9 +44,8 @@ def _sources():
     units = [(CSRC / "gw8_capi.cu", OBJ_DIR / "gw8_capi.o", [])]
     for r in range(1, 6):
         units.append((CSRC / "gw8_inst.cu", OBJ_DIR / f"gw8_inst_r{r}.o", [f"-DGW8_R={r}"]))
-    extra = CSRC / "jit_driver.cpp"
-    if extra.exists():
-        units.append((extra, OBJ_DIR / "jit_driver.o", []))
+    units.append((CSRC / "gw8_tc_inst.cu", OBJ_DIR / "gw8_tc_inst.o", []))
+    units.append((CSRC / "jit_driver.cpp", OBJ_DIR / "jit_driver.o", []))
     return units
 
 

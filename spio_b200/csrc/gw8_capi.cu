@@ -55,6 +55,7 @@ constexpr size_t kStaticScratchBytes = 4u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 unsigned char* g_static_scratch_addr[kMaxDevices] = {};  // device address, per device
 constexpr int kFwdStaticSmem = 1024;   // >= static shared memory of the kernels
+constexpr int kTcStaticSmem = 2048;    // >= static shared memory of the tcgen05 kernel
 constexpr int kAlignSlack = 1024;      // dynamic shared memory is re-aligned to 1 KiB
 
 struct DeviceInfo {
@@ -120,6 +121,10 @@ int device_info(const DeviceInfo** out) {
         return fail("cuTensorMapEncodeTiled is not available from this driver");
       g_encode = (EncodeTiledFn)fn;
     }
+    for (int r = 1; r <= 3; ++r)
+      for (int sft = 1; sft <= 3; ++sft)
+        GW8_CUDA(cudaFuncSetAttribute(gw8_tc_kernel(r, sft), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      d.smem_optin - kTcStaticSmem));
     for (const Gw8Variant& v : g_variants) {
       GW8_CUDA(cudaFuncSetAttribute(v.fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     d.smem_optin - kFwdStaticSmem));
@@ -143,6 +148,8 @@ struct Plan {
   int smem = 0;
   size_t scratch_bytes = 0;
   int n_parts = 1;  // wgrad partials per chunk
+  int engine = 1;   // 1: warp-level mma.sync kernels (v), 2: tcgen05 forward kernel (tc_kernel)
+  const void* tc_kernel = nullptr;
 };
 
 int check_shape(const spio_gw8_shape* sh) {
@@ -160,13 +167,99 @@ int check_shape(const spio_gw8_shape* sh) {
 
 // The plan needs only the SM count and the shared-memory limit, so it can be computed
 // (and unit-tested) without a device.
+// SPIO_ENGINE=1 / 2 sets the engine used when the caller leaves spio_gw8_tune.engine at 0.
+int default_engine() {
+  static const int e = [] {
+    const char* s = getenv("SPIO_ENGINE");
+    return (s != nullptr && (s[0] == '1' || s[0] == '2')) ? s[0] - '0' : 0;
+  }();
+  return e;
+}
+
+// Launch plan of the tcgen05 forward kernel: one image and one row pair per 16 KB slot of
+// 2 rows x 64 pixels, column tiles of at most 64 - (s - 1) pixels.
+int make_plan_tc(int kind, const spio_gw8_shape* sh, const spio_gw8_tune& t, int sms, int smem_optin, int p,
+                 int q, Plan* plan) {
+  if (kind == SPIO_GW8_WGRAD) return fail("engine 2 (tcgen05) computes fprop and dgrad only");
+  if (sh->r > 3 || sh->s > 3) return fail("engine 2 (tcgen05) supports filters up to 3 x 3");
+  if (t.nb > 1) return fail("engine 2 (tcgen05) streams one image per slot (nb = 1)");
+  Plan pl;
+  pl.kind = kind;
+  pl.engine = 2;
+  pl.tc_kernel = gw8_tc_kernel(sh->r, sh->s);
+  Gw8Geom& g = pl.g;
+  g.n = sh->n;
+  g.c = sh->c;
+  g.dgrad = kind == SPIO_GW8_DGRAD;
+  if (kind == SPIO_GW8_DGRAD) {
+    g.in_h = p, g.in_w = q, g.out_h = sh->h, g.out_w = sh->w;
+    g.pad_h = sh->r - 1 - sh->pad_h, g.pad_w = sh->s - 1 - sh->pad_w;
+  } else {
+    g.in_h = sh->h, g.in_w = sh->w, g.out_h = p, g.out_w = q;
+    g.pad_h = sh->pad_h, g.pad_w = sh->pad_w;
+  }
+  const int qb = cdiv(g.out_w, 8);
+  const int max_ncb = (64 - (sh->s - 1)) / 8;
+  int ncb = t.ncb;
+  if (ncb <= 0) ncb = cdiv(qb, cdiv(qb, max_ncb));
+  if (ncb > max_ncb) return fail("engine 2 (tcgen05): the column tile plus s - 1 must fit 64 pixels");
+  const int taps = sh->r * sh->s;
+  const int slot = 2 * 64 * 128, row = 64 * 128, bbytes = taps * 2048;
+  const int obuf = 2 * ncb * 8 * 128;
+  const int nob = t.nob ? t.nob : 2;
+  if (nob > 4) return fail("nob must be at most 4");
+  const int avail = smem_optin - kTcStaticSmem - kAlignSlack - row - 2 * bbytes - nob * obuf;
+  int ns = avail / slot;
+  if (ns > 12) ns = 12;
+  if (!t.ns && ns > 8) ns = 8;
+  if (t.ns) {
+    if (t.ns > ns) return fail("requested ring does not fit in shared memory");
+    ns = t.ns;
+  }
+  if (ns < 3) return fail("engine 2 (tcgen05) needs at least 3 ring slots");
+  pl.ns = ns;
+  pl.nob = nob;
+  pl.smem = kAlignSlack + ns * slot + row + 2 * bbytes + nob * obuf;
+  pl.threads = 256;
+  g.ncb = ncb;
+  g.nb = 1;
+  g.wt = 8 * ncb;
+  g.bw = 64;
+  g.in_pair_bytes = (unsigned)slot;
+  g.slot_bytes = (unsigned)slot;
+  g.out_pair_bytes = (unsigned)obuf;
+  g.obuf_bytes = (unsigned)obuf;
+  g.img_in_bytes = (unsigned)slot;
+  g.img_out_bytes = (unsigned)obuf;
+  g.n_chunks = cdiv(g.c, 64);
+  g.n_ig = g.n;
+  g.n_ct = cdiv(qb, ncb);
+  g.n_pairs = cdiv(g.out_h, 2);
+  g.n_split = 1;
+  const long long total = (long long)g.n_ig * g.n_ct * g.n_pairs * g.n_chunks;
+  if (total > 0x7fffffffLL / 2) return fail("problem too large for 32-bit work indices");
+  const int ctas = t.grid > 0 ? t.grid : sms;
+  pl.grid = (int)(total < ctas ? total : ctas);
+  *plan = pl;
+  return 0;
+}
+
 int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
               const std::vector<Gw8Variant>& variants, Plan* plan, const Gw8Variant* forced = nullptr) {
   if (check_shape(sh)) return 1;
-  static const spio_gw8_tune kAuto = {0, 0, 0, 0, 0, 0, 0, 0};
+  static const spio_gw8_tune kAuto = {0, 0, 0, 0, 0, 0, 0, 0, 0};
   const spio_gw8_tune& t = tune ? *tune : kAuto;
   const int p = sh->h + 2 * sh->pad_h - sh->r + 1;
   const int q = sh->w + 2 * sh->pad_w - sh->s + 1;
+  if (t.engine < 0 || t.engine > 2) return fail("engine must be 0, 1 or 2");
+  int engine = t.engine;
+  if (engine == 0 && forced == nullptr && !t.wpg && !t.tpw && !t.pps && t.nb <= 1 && kind != SPIO_GW8_WGRAD &&
+      sh->r <= 3 && sh->s <= 3)
+    engine = default_engine();
+  if (engine == 2) {
+    if (forced != nullptr) return fail("engine 2 (tcgen05) has no just-in-time variants");
+    return make_plan_tc(kind, sh, t, sms, smem_optin, p, q, plan);
+  }
 
   // Unless the caller asks otherwise, the forward kernel streams one row pair per slot
   // (its register window then fits without spills) and the weight-gradient kernel two.
@@ -376,11 +469,23 @@ int launch_fwd(int kind, void* out, const void* in, const void* w, const float* 
   if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
   pl.g.independent = (independent && pdl_enabled()) ? 1 : 0;
   pl.g.hint_in = hint_in;
+  if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
+  if (pl.engine == 2) {
+    const Gw8Geom& g = pl.g;
+    CUtensorMap in_map, row_map, out_map;
+    if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, 64, 2, 1)) return 1;
+    if (encode_map(&row_map, in, g.c, g.in_w, g.in_h, g.n, 64, 1, 1)) return 1;
+    if (encode_map(&out_map, out, g.c, g.out_w, g.out_h, g.n, g.wt, 2, 1)) return 1;
+    const __half* wp = static_cast<const __half*>(w);
+    int ns = pl.ns, nob = pl.nob;
+    int* status = d->status;
+    void* args[] = {&in_map, &row_map, &out_map, (void*)&g, &wp, &bias, &ns, &nob, &status};
+    return launch_kernel(pl.tc_kernel, pl.grid, pl.threads, pl.smem, stream, args);
+  }
   const Gw8Geom& g = pl.g;
   CUtensorMap in_map, out_map;
   if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
   if (encode_map(&out_map, out, g.c, g.out_w, g.out_h, g.n, g.wt, 2, g.nb)) return 1;
-  if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
   const __half* wp = static_cast<const __half*>(w);
   int ns = pl.ns, nob = pl.nob;
   int* status = d->status;
@@ -464,9 +569,10 @@ size_t act_bytes(const spio_gw8_shape* sh, bool output) {
 size_t weight_elems(const spio_gw8_shape* sh) { return (size_t)sh->c * sh->r * sh->s * 8; }
 
 void fill_info(const Plan& pl, spio_gw8_plan_info* info) {
-  info->wpg = pl.v->wpg;
-  info->tpw = pl.v->tpw;
-  info->pps = pl.v->pps;
+  info->engine = pl.engine;
+  info->wpg = pl.v ? pl.v->wpg : 0;
+  info->tpw = pl.v ? pl.v->tpw : 0;
+  info->pps = pl.v ? pl.v->pps : 1;
   info->ns = pl.ns;
   info->nob = pl.nob;
   info->ncb = pl.g.ncb;

@@ -21,6 +21,7 @@ struct Gw8Tune {
   int nb;   // images per slot
   int grid; // CTAs (0: one per SM)
   int pps;  // row pairs per ring slot (compiled variants only)
+  int engine;  // 0 auto, 1 warp-level mma.sync kernels, 2 tcgen05 forward kernel
 };
 
 struct Gw8Variant {
@@ -36,5 +37,8 @@ int gw8_variants_r2(const Gw8Variant** out);
 int gw8_variants_r3(const Gw8Variant** out);
 int gw8_variants_r4(const Gw8Variant** out);
 int gw8_variants_r5(const Gw8Variant** out);
+
+// conv2d_gw8_fwd_tc_kernel<Gw8TcConfig<r, s>> for 1 <= r, s <= 3, else NULL.
+const void* gw8_tc_kernel(int r, int s);
 
 }  // namespace spio_b200

@@ -1,5 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a building blocks the gw8 kernels use:
 // mbarrier (with time-bounded waits), TMA tiled loads/stores (never multicast),
+// tcgen05 tensor-core instructions with accumulators in tensor memory,
 // ldmatrix / stmatrix and warp-level mma.sync with fp32 accumulation.
 //
 // The file is device-only and includes no host headers, so the same text compiles
@@ -199,6 +200,82 @@ __device__ __forceinline__ void tma_store_wait_read0() {
 // Until every committed store has completed.
 __device__ __forceinline__ void tma_store_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- tcgen05 (5th-generation tensor cores)
+
+// Tensor memory: 128 lanes x 512 columns of 32 bits per SM.  A warp allocates a power-of-two
+// number of columns (>= 32); the base address (lane in bits 31:16, column in bits 15:0) is
+// written to shared memory.  The same warp must free it before the CTA exits.
+__device__ __forceinline__ void tmem_alloc(u32 holder_smem, u32 columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem),
+               "r"(columns)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(u32 taddr, u32 columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes apart
+// and stored with the 128-byte swizzle (the layout a tiled TMA load with SWIZZLE_128B writes):
+// groups of 8 rows are 1024 bytes apart.  The swizzle is a function of the absolute address,
+// so `addr` may point at any row (a multiple of 128 bytes) and any 32-byte k-step of a row.
+__device__ __forceinline__ u64 umma_desc_k_sw128(u32 addr) {
+  return (u64)((addr >> 4) & 0x3fffu)  // start address / 16
+         | ((u64)1u << 16)             // leading byte offset: not used by swizzled K-major tiles
+         | ((u64)(1024u >> 4) << 32)   // stride byte offset between 8-row groups / 16
+         | ((u64)1u << 46)             // descriptor version of sm_100
+         | ((u64)2u << 61);            // 128-byte swizzle
+}
+
+// Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, tile M x N (K = 16).
+__device__ __forceinline__ constexpr u32 umma_idesc_f16_f32(int m, int n) {
+  return (1u << 4) | ((u32)(n >> 3) << 17) | ((u32)(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, issued by ONE thread; completion is observed through
+// tcgen05_commit.
+__device__ __forceinline__ void umma_f16_ss(u32 d_tmem, u64 a_desc, u64 b_desc, u32 idesc, u32 accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The mbarrier receives one arrival once every tcgen05 operation issued so far by this thread
+// has completed.
+__device__ __forceinline__ void tcgen05_commit(u32 bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+// 32 lanes x 32 consecutive columns -> 32 registers per thread (thread t reads lane base + t).
+__device__ __forceinline__ void tmem_ld_32x32(u32 (&v)[32], u32 taddr) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+        "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+        "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+        "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- ldmatrix / stmatrix
