@@ -10,19 +10,26 @@
 //
 //  * a ring slot is one row pair of one image: 2 rows x 64 pixels x 64 channels, each pixel
 //    one 128-byte row of a K-major, 128-byte-swizzled operand tile;
-//  * an output row pair is ONE accumulator tile D[128 pixels][64 channels] (fp32, 64 columns
-//    of tensor memory).  For tap (r, s) the A operand is the 128 consecutive pixel rows that
-//    start at input row r, pixel s of the window: a shared-memory descriptor that points
-//    into the ring at a shifted address, nothing is copied;
-//  * the group structure is block-diagonal weights: channels 16j..16j+15 (two groups) of tap
-//    (r, s) multiply B_{r,s,j}[16 out][16 in] (two 8x8 blocks on the diagonal) into columns
-//    16j..16j+15 of D: R*S*4 instructions of shape M128 N16 K16 per row pair, issued by one
-//    thread;
+//  * an output row pair is ONE accumulator tile of 128 pixels (fp32, in tensor memory).  A
+//    tcgen05.mma of this shape takes about 75 cycles whatever its N (measured for N = 16..128),
+//    and K is fixed at 16, so the instruction count decides: shifting the A operand for each
+//    of the R*S taps would cost R*S*4 instructions per tile, twice the time the HBM stream
+//    leaves.  Only the VERTICAL taps shift A (a shared-memory descriptor that points into the
+//    ring at input row r of the window; nothing is copied).  The S horizontal taps of a row
+//    are computed side by side in N from the same unshifted A,
+//        D[p][s][k] = sum_r sum_c x[row + r][p][c] * w[k][r][s][c],
+//    and the shift moves to the output side, y[p][k] = sum_s D[p + s][s][k], which the
+//    epilogue does with warp shuffles: R*4 instructions of shape M128 N(16*S) K16 per tile;
+//  * the group structure is block-diagonal weights: channels 16j..16j+15 (two groups) multiply
+//    B_{r,j}[S*16 (s, out)][16 in], two 8x8 blocks on the diagonal per s, into columns
+//    j*16*S .. of D; the instructions are issued by one thread;
 //  * the window of R+1 input rows spans two ring slots; where the ring wraps, the first row
 //    of slot 0 is loaded a second time behind the last slot so that the 128 rows of every
 //    tap stay contiguous;
-//  * four epilogue warps read the accumulator (one pixel per thread), add the bias, round to
-//    fp16 and write swizzled 128-byte pixel rows into a staging buffer for the TMA store.
+//  * sixteen epilogue warps read the accumulator (one pixel and 16 channels per thread), add the S shifted
+//    partial sums (the two pixels past a warp's 32 lanes come from the next warp through
+//    shared memory), add the bias, round to fp16 and write swizzled 128-byte pixel rows
+//    into a staging buffer for the TMA store.
 //
 // Restrictions (the launch planner falls back to the mma.sync kernel otherwise): R, S <= 3,
 // column tile + S - 1 <= 64 pixels, one image per slot.
@@ -35,6 +42,7 @@
 #include "gw8_common.cuh"
 
 namespace spio_b200 {
+
 
 enum { TC_END = 1, TC_HAS_OUT = 2, TC_SEG_LAST = 4 };
 
@@ -53,9 +61,10 @@ template <int R_, int S_>
 struct Gw8TcConfig {
   static constexpr int R = R_, S = S_, NT = R_ * S_;
   static constexpr int E = R_ / 2;          // stages of lead-in per segment
-  static constexpr int THREADS = 256;       // load, mma, weights, store, 4 x epilogue
-  static constexpr int NACC = 4;            // accumulator tiles in tensor memory
-  static constexpr int TMEM_COLS = 256;     // NACC * 64
+  static constexpr int THREADS = 640;       // load, mma, weights, store, 16 x epilogue
+  static constexpr int ACC_COLS = 64 * S_;                 // columns of one accumulator tile
+  static constexpr int NACC = S_ == 3 ? 2 : 4;             // accumulator tiles in tensor memory
+  static constexpr int TMEM_COLS = S_ == 1 ? 256 : 512;    // power of two >= NACC * ACC_COLS
   static constexpr int SLOT_BYTES = 2 * 64 * 128;
   static constexpr int ROW_BYTES = 64 * 128;
   static constexpr int B_BYTES = NT * 2048;  // per chunk: NT taps x 16 rows x 128 bytes
@@ -72,7 +81,10 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
   constexpr int MAX_NS = 12, MAX_NOB = 4;
 
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) u64 bars[2 * MAX_NS + 2 * NACC + 4 + 2 * MAX_NOB];
+  __shared__ __align__(8) u64 bars[2 * MAX_NS + 2 * NACC + 4 + 2 * MAX_NOB + 32];
+  // what lanes 30 and 31 of an even quarter need from the odd quarter after it:
+  // [warp pair][tile parity][0: X30, 1: X31][channel]
+  __shared__ float xch[2][2][2][64];
   __shared__ Gw8TcDesc desc[MAX_NS];
   __shared__ Gw8TcDesc tdesc[NACC];
   __shared__ Gw8TcDesc odesc[MAX_NOB];
@@ -93,6 +105,12 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
   auto b_empty = [&](int i) { return bar0 + 8u * (u32)(2 * MAX_NS + 2 * NACC + 2 + i); };
   auto ofull = [&](int i) { return bar0 + 8u * (u32)(2 * MAX_NS + 2 * NACC + 4 + i); };
   auto oempty = [&](int i) { return bar0 + 8u * (u32)(2 * MAX_NS + 2 * NACC + 4 + MAX_NOB + i); };
+  auto xfull = [&](int pair, int cq, int par) {
+    return bar0 + 8u * (u32)(2 * MAX_NS + 2 * NACC + 4 + 2 * MAX_NOB + 8 * pair + 2 * cq + par);
+  };
+  auto xempty = [&](int pair, int cq, int par) {
+    return bar0 + 8u * (u32)(2 * MAX_NS + 2 * NACC + 20 + 2 * MAX_NOB + 8 * pair + 2 * cq + par);
+  };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -104,15 +122,19 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
     }
     for (int i = 0; i < NACC; ++i) {
       mbar_init(acc_full(i), 2);   // the issuing thread (descriptor written) + tcgen05.commit
-      mbar_init(acc_empty(i), 4);  // the four epilogue warps
+      mbar_init(acc_empty(i), 16);  // the sixteen epilogue warps
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(b_full(i), 1);
       mbar_init(b_empty(i), 1);
     }
     for (int i = 0; i < nob; ++i) {
-      mbar_init(ofull(i), 4);
+      mbar_init(ofull(i), 16);
       mbar_init(oempty(i), 1);
+    }
+    for (int i = 0; i < 16; ++i) {
+      mbar_init(xfull(i >> 3, (i >> 1) & 3, i & 1), 1);
+      mbar_init(xempty(i >> 3, (i >> 1) & 3, i & 1), 1);
     }
     abort_flag = 0;
     mbar_fence_init();
@@ -183,7 +205,7 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA warp (one thread issues)
     if (lane == 0) {
-      constexpr u32 IDESC = umma_idesc_f16_f32(128, 16);
+      constexpr u32 IDESC = umma_idesc_f16_f32(128, 16 * S);
       int slot = 0, prev = 0, ab = 0, bq = -1, cur_ck = -1;
       u32 par = 0, apar = 0;
       for (;;) {
@@ -207,7 +229,7 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
         if (d.flags & TC_HAS_OUT) {
           if (!mbar_wait(acc_empty(ab), apar ^ 1u, abortp)) break;
           tcgen05_fence_after_sync();
-          const u32 d_tmem = tmem + (u32)ab * 64u;
+          const u32 d_tmem = tmem + (u32)ab * (u32)Cfg::ACC_COLS;
           const u32 bb = bbuf + (u32)(bq & 1) * BB;
           const u32 a_prev = ring + (u32)prev * SLOT, a_cur = ring + (u32)slot * SLOT;
 #pragma unroll
@@ -216,13 +238,9 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
             // without lead-in (R = 1) the window is this slot
             const u32 a_row = E == 0 ? a_cur : (r < 2 ? a_prev + (u32)r * ROW : a_cur + (u32)(r - 2) * ROW);
 #pragma unroll
-            for (int s = 0; s < S; ++s) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                umma_f16_ss(d_tmem + 16u * (u32)j, umma_desc_k_sw128(a_row + (u32)s * 128u + 32u * (u32)j),
-                            umma_desc_k_sw128(bb + (u32)(r * S + s) * 2048u + 32u * (u32)j), IDESC,
-                            (r | s) != 0 ? 1u : 0u);
-            }
+            for (int j = 0; j < 4; ++j)  // channels 16j..16j+15 -> columns j*16*S.. (all S horizontal taps)
+              umma_f16_ss(d_tmem + (u32)(16 * S * j), umma_desc_k_sw128(a_row + 32u * (u32)j),
+                          umma_desc_k_sw128(bb + (u32)(r * S) * 2048u + 32u * (u32)j), IDESC, r != 0 ? 1u : 0u);
           }
           tdesc[ab] = d;
           mbar_arrive(acc_full(ab));     // orders the descriptor before the epilogue's read
@@ -302,11 +320,18 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    // Thread (quarter q, lane l) owns pixel p = 32q + l of the tile: row p / 64, column p % 64.
-    const int quarter = warp & 3;
+    // Sixteen warps: warp (quarter q = warp % 4, channel block cq) owns pixels 32q..32q+31 of
+    // the tile (thread = pixel p = 32q + lane: row p / 64, column p % 64) and channels
+    // 16cq..16cq+15.  y[p] = sum_s D[p + s][s]: the partial sums of the next one or two pixels
+    // come from the neighbouring lanes by shuffle.  Lanes 30, 31 of an even quarter lack
+    // pixels 32, 33, which belong to the odd quarter that follows; that warp leaves
+    // X30 = D[32][2] and X31 = D[32][1] + D[33][2] in shared memory for them.  (The last lanes
+    // of an odd quarter are columns 62, 63 of the 64-pixel row, which are never stored.)
+    const int quarter = warp & 3, pair = quarter >> 1, cq = (warp - 4) >> 2;
+    const bool odd = (quarter & 1) != 0;
     const int p = 32 * quarter + lane;
     const int row = p >> 6, col = p & 63;
-    int ab = 0, ob = 0;
+    int ab = 0, ob = 0, tile = 0;
     u32 apar = 0, opar = 0;
     for (;;) {
       if (!mbar_wait(acc_full(ab), apar, abortp)) break;
@@ -326,31 +351,62 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
         break;
       }
       tcgen05_fence_after_sync();
-      u32 v[2][32];
-      const u32 t_addr = tmem + ((u32)(32 * quarter) << 16) + (u32)ab * 64u;
-      tmem_ld_32x32(v[0], t_addr);
-      tmem_ld_32x32(v[1], t_addr + 32u);
+      const u32 t_base = tmem + ((u32)(32 * quarter) << 16) + (u32)ab * (u32)Cfg::ACC_COLS + (u32)(16 * S * cq);
+      const int xp = tile & 1;                     // exchange buffer of this tile
+      const u32 xpar = (u32)(tile >> 1) & 1u;      // parity of this use of the buffer
+      u32 v[S][16];  // partial sums of this thread's pixel: v[s][k], channel 16cq + k
+#pragma unroll
+      for (int s = 0; s < S; ++s) tmem_ld_32x16(v[s], t_base + (u32)(16 * s));
       tmem_ld_wait();
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty(ab));  // the accumulator tile is free again
+      if (S > 1 && odd) {
+        if (!mbar_wait(xempty(pair, cq, xp), xpar ^ 1u, abortp)) break;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float x31 = __uint_as_float(v[1][k]);
+          if (S > 2) x31 += __shfl_down_sync(0xffffffffu, __uint_as_float(v[S > 2 ? 2 : 0][k]), 1);
+          if (lane == 0) {
+            xch[pair][xp][1][16 * cq + k] = x31;
+            if (S > 2) xch[pair][xp][0][16 * cq + k] = __uint_as_float(v[S > 2 ? 2 : 0][k]);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xfull(pair, cq, xp));
+      }
+      float f[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        f[k] = __uint_as_float(v[0][k]);
+        if (S > 1) shfl_down_add(f[k], __uint_as_float(v[S > 1 ? 1 : 0][k]), 1);
+        if (S > 2) shfl_down_add(f[k], __uint_as_float(v[S > 2 ? 2 : 0][k]), 2);
+      }
+      if (S > 1 && !odd) {
+        if (!mbar_wait(xfull(pair, cq, xp), xpar, abortp)) break;
+        if (lane >= (S > 2 ? 30 : 31)) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) f[k] += xch[pair][xp][lane - 30][16 * cq + k];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xempty(pair, cq, xp));
+      }
       if (!mbar_wait(oempty(ob), opar ^ 1u, abortp)) break;
       if (col < g.wt) {
         unsigned char* const dst = smem + (obufs - ring) + (u32)ob * g.obuf_bytes + (u32)(row * g.wt + col) * 128u;
         const float* const bp = bias != nullptr ? bias + d.ck * 64 : nullptr;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {  // 16-byte piece c: channels 8c..8c+7 of the chunk
-          float f[8];
-#pragma unroll
-          for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(v[(8 * c + k) >> 5][(8 * c + k) & 31]);
+        for (int h = 0; h < 2; ++h) {  // 16-byte piece c = 2cq + h: channels 8c..8c+7 of the chunk
+          const int c = 2 * cq + h;
+          float* const e = f + 8 * h;
           if (bp != nullptr && d.ck * 64 + 8 * c < g.c) {
             const float4 b0 = __ldg(reinterpret_cast<const float4*>(bp + 8 * c));
             const float4 b1 = __ldg(reinterpret_cast<const float4*>(bp + 8 * c + 4));
-            f[0] += b0.x, f[1] += b0.y, f[2] += b0.z, f[3] += b0.w;
-            f[4] += b1.x, f[5] += b1.y, f[6] += b1.z, f[7] += b1.w;
+            e[0] += b0.x, e[1] += b0.y, e[2] += b0.z, e[3] += b0.w;
+            e[4] += b1.x, e[5] += b1.y, e[6] += b1.z, e[7] += b1.w;
           }
-          const __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
-          const __half2 h2 = __floats2half2_rn(f[4], f[5]), h3 = __floats2half2_rn(f[6], f[7]);
+          const __half2 h0 = __floats2half2_rn(e[0], e[1]), h1 = __floats2half2_rn(e[2], e[3]);
+          const __half2 h2 = __floats2half2_rn(e[4], e[5]), h3 = __floats2half2_rn(e[6], e[7]);
           uint4 o;
           o.x = *reinterpret_cast<const u32*>(&h0);
           o.y = *reinterpret_cast<const u32*>(&h1);
@@ -371,6 +427,7 @@ conv2d_gw8_fwd_tc_body(const TensorMap& in_map, const TensorMap& row_map, const 
         ab = 0;
         apar ^= 1u;
       }
+      ++tile;
     }
   }
 

@@ -55,7 +55,7 @@ constexpr size_t kStaticScratchBytes = 4u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 unsigned char* g_static_scratch_addr[kMaxDevices] = {};  // device address, per device
 constexpr int kFwdStaticSmem = 1024;   // >= static shared memory of the kernels
-constexpr int kTcStaticSmem = 2048;    // >= static shared memory of the tcgen05 kernel
+constexpr int kTcStaticSmem = 6144;    // >= static shared memory of the tcgen05 kernel
 constexpr int kAlignSlack = 1024;      // dynamic shared memory is re-aligned to 1 KiB
 
 struct DeviceInfo {
@@ -220,7 +220,7 @@ int make_plan_tc(int kind, const spio_gw8_shape* sh, const spio_gw8_tune& t, int
   pl.ns = ns;
   pl.nob = nob;
   pl.smem = kAlignSlack + ns * slot + row + 2 * bbytes + nob * obuf;
-  pl.threads = 256;
+  pl.threads = 640;
   g.ncb = ncb;
   g.nb = 1;
   g.wt = 8 * ncb;

@@ -24,3 +24,4 @@ const void* gw8_tc_kernel(int r, int s) {
 }
 
 }  // namespace spio_b200
+

@@ -274,8 +274,29 @@ __device__ __forceinline__ void tmem_ld_32x32(u32 (&v)[32], u32 taddr) {
       : "r"(taddr));
 }
 
+// The same for 16 consecutive columns.
+__device__ __forceinline__ void tmem_ld_32x16(u32 (&v)[16], u32 taddr) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+        "=r"(v[15])
+      : "r"(taddr));
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// acc += the value of lane (own lane + delta), skipped where that lane does not exist.
+__device__ __forceinline__ void shfl_down_add(float& acc, float v, int delta) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .f32 t;\n\t"
+      "shfl.sync.down.b32 t|p, %1, %2, 31, 0xffffffff;\n\t"
+      "@p add.f32 %0, %0, t;\n\t}"
+      : "+f"(acc)
+      : "f"(v), "r"(delta));
 }
 
 // ---------------------------------------------------------------- ldmatrix / stmatrix

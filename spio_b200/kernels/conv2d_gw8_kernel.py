@@ -8,9 +8,11 @@ configuration fixes the warp mapping and the ring instead:
     wpg  compute warps per channel group        tpw  8-pixel x 2-row tiles per warp
     pps  row pairs per ring slot                 ncb  8-pixel column blocks per column tile
     nb   images per ring slot                    ns   ring slots
-    nob  output staging buffers
+    nob  output staging buffers                   engine  1 = warp-level mma.sync kernel,
+                                                          2 = tcgen05 kernel (tensor memory)
 
-A zero means "let the launch planner choose".
+A zero means "let the launch planner choose".  Engine 2 exists for filters up to 3 x 3; it
+takes ncb, ns and nob only.
 """
 
 from __future__ import annotations
@@ -36,6 +38,7 @@ class Conv2dGw8Config:
     nb: int = 0
     ns: int = 0
     nob: int = 0
+    engine: int = 0
 
     def as_tune(self) -> dict:
         return asdict(self)
@@ -95,6 +98,15 @@ def _get_configs(params: Conv2dGw8Params, device_attr, igrad: bool = False) -> I
             for ns in (0, 3, 4, 6):
                 for nob in (2, 3):
                     cfg = Conv2dGw8Config(wpg=wpg, tpw=tpw, pps=pps, ncb=ncb, nb=nb, ns=ns, nob=nob)
+                    if plan_is_valid(kind, params, cfg.as_tune(), device_attr):
+                        yield cfg
+    if params.r <= 3 and params.s <= 3:
+        # the tcgen05 kernel: column tiles of up to 64 - (s - 1) pixels, ring depth, staging buffers
+        for n_ct in range(1, 4):
+            ncb = divup(divup(out_w, 8), n_ct)
+            for ns in (0, 4, 6):
+                for nob in (2, 3):
+                    cfg = Conv2dGw8Config(engine=2, ncb=ncb, ns=ns, nob=nob)
                     if plan_is_valid(kind, params, cfg.as_tune(), device_attr):
                         yield cfg
 

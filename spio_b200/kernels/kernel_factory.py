@@ -17,9 +17,11 @@ from .kernel import Kernel, get_full_kernel_name
 def _wants_jit(params, config) -> bool:
     from ..compiler import flags
 
+    tune = config.as_tune() if config is not None else {}
+    if tune.get("engine", 0) == 2:
+        return False  # the tcgen05 kernel is built into the library only
     if flags.jit.get():
         return True
-    tune = config.as_tune() if config is not None else {}
     wpg, tpw, pps = (tune.get(k, 0) for k in ("wpg", "tpw", "pps"))
     if not (wpg and tpw and pps):
         return False

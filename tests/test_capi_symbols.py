@@ -31,8 +31,8 @@ def test_header_symbols_are_exported_and_bound():
 
 def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(_clib.Shape) == 8 * 4
-    assert ctypes.sizeof(_clib.Tune) == 8 * 4
-    assert ctypes.sizeof(_clib.PlanInfo) == 16 * 4 + 8  # 15 ints, 4 bytes of padding, size_t
+    assert ctypes.sizeof(_clib.Tune) == 9 * 4
+    assert ctypes.sizeof(_clib.PlanInfo) == 16 * 4 + 8  # 16 ints, size_t
 
 
 def plan(kind, sh, tune=None):
@@ -96,3 +96,24 @@ def test_headline_plan():
     assert rc == 0 and p["grid"] == 148 and p["ncb"] == 7 and p["nb"] == 1 and p["n_pairs"] == 28
     rc, p = plan(_clib.WGRAD, Shape(2048, 64, 56, 56))
     assert rc == 0 and p["n_split"] == 148 and p["grid"] == 148
+
+
+def test_planner_engine_2():
+    """The tcgen05 forward kernel: 640 threads, one image and one 64-pixel row pair per slot."""
+    from oracle.oracle import Shape
+
+    sh = Shape(256, 64, 56, 56, 3, 3, 1, 1)
+    rc, p = plan(_clib.FPROP, sh, {"engine": 2})
+    assert rc == 0 and p["engine"] == 2 and p["threads"] == 640
+    assert (p["ncb"], p["nb"], p["pps"], p["n_col_tiles"]) == (7, 1, 1, 1)
+    assert 3 <= p["ns"] <= 8 and p["nob"] == 2
+    assert p["smem_bytes"] == 1024 + p["ns"] * 16384 + 8192 + 2 * 9 * 2048 + 2 * 2 * 56 * 128
+    assert p["smem_bytes"] <= SMEM - 6144
+    rc, p = plan(_clib.DGRAD, Shape(8, 128, 20, 130, 1, 3, 0, 1), {"engine": 2})
+    assert rc == 0 and p["n_col_tiles"] == 3 and p["n_chunks"] == 2
+    rc, p = plan(_clib.FPROP, sh, None)
+    assert rc == 0 and p["engine"] == 1
+    assert plan(_clib.WGRAD, sh, {"engine": 2})[0] != 0
+    assert plan(_clib.FPROP, Shape(8, 64, 20, 20, 5, 5, 2, 2), {"engine": 2})[0] != 0
+    assert plan(_clib.FPROP, sh, {"engine": 2, "ncb": 8})[0] != 0
+    assert plan(_clib.FPROP, sh, {"engine": 3})[0] != 0
