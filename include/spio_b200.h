@@ -195,6 +195,22 @@ int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const 
 int spio_conv2d_gw8_wgrad_reduce(float* dw, float* dbias, const float* scratch, int c, int taps, int n_parts,
                                  void* stream);
 
+/* ---- LayerNorm2d ---------------------------------------------------------------------
+ * LayerNorm over the channels of an NHWC fp16 tensor, the op that follows the gw8 convolution
+ * in a ConvNeXt block.  rows = n * h * w pixels of c channels (c a multiple of 8, at most 1024);
+ * weight / bias are fp32 [c] or NULL; statistics are fp32.  The forward pass covers the
+ * reference's kernel spio/src/layernorm_2d.cu:82-221 (which the reference ships but wires to no
+ * operator); the backward pass has no counterpart there.
+ *   fwd: y = (x - mean) * rstd * weight + bias; stats[row] = {mean, rstd} if stats != NULL.
+ *   bwd: dx from dy, x, stats and weight; dweight / dbias (fp32 [c], may be NULL) are summed
+ *        over all pixels through `scratch` (spio_layernorm_2d_bwd_scratch_bytes) in a fixed order. */
+int spio_layernorm_2d_fwd(void* y, float* stats, const void* x, const float* weight, const float* bias,
+                          long long rows, int c, float eps, void* stream);
+size_t spio_layernorm_2d_bwd_scratch_bytes(long long rows, int c);
+int spio_layernorm_2d_bwd(void* dx, float* dweight, float* dbias, const void* dy, const void* x,
+                          const float* stats, const float* weight, long long rows, int c, void* scratch,
+                          size_t scratch_bytes, void* stream);
+
 /* Number of compiled (r, s, wpg, tpw, pps) variants, and the i-th one. */
 int spio_conv2d_gw8_num_variants(void);
 int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw, int* pps);

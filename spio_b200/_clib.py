@@ -8,7 +8,7 @@ or fails to load, every operator raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_size_t, c_ulonglong, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p
 from pathlib import Path
 from typing import Optional
 
@@ -102,6 +102,12 @@ SIGNATURES = {
     "spio_conv2d_gw8_prepare_launch": (
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_void_p, c_void_p, POINTER(Launch)]),
     "spio_conv2d_gw8_wgrad_reduce": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "spio_layernorm_2d_fwd": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_float, c_void_p]),
+    "spio_layernorm_2d_bwd_scratch_bytes": (c_size_t, [c_longlong, c_int]),
+    "spio_layernorm_2d_bwd": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+                c_void_p, c_size_t, c_void_p]),
     "spio_conv2d_gw8_num_variants": (c_int, []),
     "spio_conv2d_gw8_variant": (
         c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),

@@ -46,6 +46,7 @@ def _sources():
         units.append((CSRC / "gw8_inst.cu", OBJ_DIR / f"gw8_inst_r{r}.o", [f"-DGW8_R={r}"]))
     units.append((CSRC / "gw8_tc_inst.cu", OBJ_DIR / "gw8_tc_inst.o", []))
     units.append((CSRC / "jit_driver.cpp", OBJ_DIR / "jit_driver.o", []))
+    units.append((CSRC / "layernorm_2d.cu", OBJ_DIR / "layernorm_2d.o", []))
     return units
 
 

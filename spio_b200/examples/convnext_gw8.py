@@ -63,6 +63,20 @@ class ConvNeXtGw8(nn.Module):
         return self.head(self.head_norm(x))
 
 
+def swap_layernorm(model: nn.Module) -> int:
+    """Replace every channel LayerNorm of the network (the LayerNorm2d wrapper above) by the
+    fused ``spio_b200.layers.LayerNorm2d``; returns how many were replaced."""
+    from spio_b200.layers import LayerNorm2d as FusedLayerNorm2d
+
+    count = 0
+    for parent in model.modules():
+        for name, child in list(parent.named_children()):
+            if isinstance(child, LayerNorm2d) and FusedLayerNorm2d.match(child.norm):
+                setattr(parent, name, FusedLayerNorm2d.from_torch_module(child.norm))
+                count += 1
+    return count
+
+
 def train_step(model: nn.Module, images: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
     """Forward + backward under fp16 autocast; returns the loss."""
     with torch.autocast("cuda", dtype=torch.float16):
@@ -83,8 +97,14 @@ def main() -> None:
     model = ConvNeXtGw8().to(dev).to(memory_format=torch.channels_last)
     images = torch.randn(args.batch, 3, 224, 224, device=dev).contiguous(memory_format=torch.channels_last)
     labels = torch.randint(0, 1000, (args.batch,), device=dev)
+    import copy
+
     fast, replaced = _transform(model)
-    for name, net in (("torch / cuDNN grouped conv", model), (f"spio_b200 ({replaced} layers swapped)", fast)):
+    with_ln = copy.deepcopy(model)
+    n_ln = swap_layernorm(with_ln)          # before tracing: transform keeps the fused modules
+    fused, _ = _transform(with_ln)
+    for name, net in (("torch / cuDNN grouped conv", model), (f"spio_b200 ({replaced} layers swapped)", fast),
+                      (f"spio_b200 ({replaced} convs + {n_ln} LayerNorm2d swapped)", fused)):
         for _ in range(2):
             net.zero_grad(set_to_none=True)
             train_step(net, images, labels)

@@ -43,3 +43,38 @@ def test_scan_modules_lists_the_gw8_layers():
     shapes = scan_modules(model, torch.randn(2, 3, 64, 64))
     assert [(p.c, p.h) for p in shapes] == [(96, 16), (192, 8), (384, 4), (768, 2)]
     assert all(p.r == 3 and p.has_bias for p in shapes)
+
+
+@pytest.mark.gpu
+def test_convnext_train_step_with_fused_layernorm():
+    """Swapping the channel LayerNorms for spio_b200.layers.LayerNorm2d keeps loss and
+    gradients of the train step within fp16 tolerance of the torch LayerNorm path."""
+    from spio_b200.examples.convnext_gw8 import swap_layernorm
+    from spio_b200.layers import LayerNorm2d
+
+    torch.manual_seed(1234 + 4)
+    dev = torch.device("cuda")
+    model = ConvNeXtGw8().to(dev).to(memory_format=torch.channels_last)
+    images = torch.randn(8, 3, 224, 224, device=dev).contiguous(memory_format=torch.channels_last)
+    labels = torch.randint(0, 1000, (8,), device=dev)
+    fast, _ = _transform(model)
+    ref_loss = train_step(fast, images, labels)
+    ref_grads = {id(p): p.grad.clone() for p in fast.parameters()}   # parameters are shared, not copied
+    fast.zero_grad(set_to_none=True)
+
+    swapped = swap_layernorm(model)
+    assert swapped == 22  # stem + 3 downsampling + 18 blocks
+    fused, replaced = _transform(model)
+    assert replaced == 18
+    assert sum(isinstance(m, LayerNorm2d) for m in model.modules()) == 22
+    # tracing looks through the layer, so the transformed graph calls the operator directly
+    assert sum("layernorm_2d" in str(n.target) for n in fused.graph.nodes if n.op == "call_function") == 22
+    loss = train_step(fused, images, labels)
+    assert device_status() == 0
+    assert abs(float(loss) - float(ref_loss)) <= 2e-2 * abs(float(ref_loss))
+    worst, checked = 0.0, 0
+    for p in fused.parameters():
+        r = ref_grads[id(p)].float()
+        worst = max(worst, float((p.grad.float() - r).abs().max()) / (float(r.abs().max()) + 1e-12))
+        checked += 1
+    assert checked == len(ref_grads) and worst <= 8e-2, worst

@@ -168,3 +168,27 @@ def test_util_helpers():
     assert_all_close_with_acc_depth(a, a + 1e-5, acc_depth=72)
     with pytest.raises(AssertionError, match="Tensors not close"):
         assert_all_close_with_acc_depth(a, a + 1.0, acc_depth=72, msg="ctx")
+
+
+def test_layernorm_2d_layer_and_op_checks():
+    """Host-side behaviour of LayerNorm2d that needs no GPU."""
+    import torch
+    from torch import nn
+
+    from spio_b200.functional import layernorm_2d
+    from spio_b200.layers import LayerNorm2d
+
+    ln = LayerNorm2d(96, eps=1e-5)
+    assert ln.weight.shape == (96,) and ln.bias.dtype == torch.float32 and "96" in repr(ln)
+    assert LayerNorm2d(64, elementwise_affine=False).weight is None
+    assert LayerNorm2d.match(nn.LayerNorm(192)) and not LayerNorm2d.match(nn.LayerNorm(100))
+    assert not LayerNorm2d.match(nn.LayerNorm((4, 8))) and not LayerNorm2d.match(nn.BatchNorm2d(64))
+    src = nn.LayerNorm(384, eps=1e-6)
+    assert LayerNorm2d.from_torch_module(src).weight is src.weight
+    with pytest.raises(ValueError):
+        LayerNorm2d(12)
+    with pytest.raises(Exception, match="CUDA"):
+        layernorm_2d(torch.zeros(1, 64, 2, 2, dtype=torch.float16))
+    # fake (meta) implementation: shapes and dtypes without a device
+    y, stats = torch.ops.spio.layernorm_2d(torch.empty(2, 64, 3, 5, dtype=torch.float16, device="meta"), None, None, 1e-6)
+    assert y.shape == (2, 64, 3, 5) and stats.shape == (30, 2) and stats.dtype == torch.float32
