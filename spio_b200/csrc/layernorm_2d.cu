@@ -48,6 +48,19 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
+// f = p[8 * piece .. 8 * piece + 7], or `fill` when p is NULL or the piece is out of range.
+__device__ __forceinline__ void load8(float (&f)[8], const float* __restrict__ p, int piece, int pieces,
+                                      float fill) {
+  if (p != nullptr && piece < pieces) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p) + 2 * piece);
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 2 * piece + 1);
+    f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = fill;
+  }
+}
+
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   uint4 u;
   __half2* h = reinterpret_cast<__half2*>(&u);
@@ -58,7 +71,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 
 // K = pieces per lane, t = lanes per pixel (power of two), pieces = c / 8.
 template <int K>
-__global__ void __launch_bounds__(kLnThreads)
+__global__ void __launch_bounds__(kLnThreads, 2)
 layernorm_2d_fwd_kernel(uint4* __restrict__ y, float2* __restrict__ stats, const uint4* __restrict__ x,
                         const float* __restrict__ weight, const float* __restrict__ bias, long long rows,
                         int pieces, int t, float inv_c, float eps) {
@@ -76,11 +89,8 @@ layernorm_2d_fwd_kernel(uint4* __restrict__ y, float2* __restrict__ stats, const
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int piece = lane_in_group + k * t;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      w[k][i] = (weight != nullptr && piece < pieces) ? weight[piece * 8 + i] : 1.f;
-      b[k][i] = (bias != nullptr && piece < pieces) ? bias[piece * 8 + i] : 0.f;
-    }
+    load8(w[k], weight, piece, pieces, 1.f);
+    load8(b[k], bias, piece, pieces, 0.f);
   }
 
   for (long long base = warp_first; base < rows; base += warp_step) {
@@ -128,7 +138,7 @@ layernorm_2d_fwd_kernel(uint4* __restrict__ y, float2* __restrict__ stats, const
 
 // Partials: part[cta][0][c] = sum of dy * xhat, part[cta][1][c] = sum of dy over the CTA's pixels.
 template <int K>
-__global__ void __launch_bounds__(kLnThreads)
+__global__ void __launch_bounds__(kLnThreads, 2)
 layernorm_2d_bwd_kernel(uint4* __restrict__ dx, float* __restrict__ part, const uint4* __restrict__ dy,
                         const uint4* __restrict__ x, const float2* __restrict__ stats,
                         const float* __restrict__ weight, long long rows, int pieces, int t, float inv_c) {
@@ -146,13 +156,9 @@ layernorm_2d_bwd_kernel(uint4* __restrict__ dx, float* __restrict__ part, const 
   float w[K][8], gw[K][8], gb[K][8];
 #pragma unroll
   for (int k = 0; k < K; ++k) {
-    const int piece = lane_in_group + k * t;
+    load8(w[k], weight, lane_in_group + k * t, pieces, 1.f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      w[k][i] = (weight != nullptr && piece < pieces) ? weight[piece * 8 + i] : 1.f;
-      gw[k][i] = 0.f;
-      gb[k][i] = 0.f;
-    }
+    for (int i = 0; i < 8; ++i) gw[k][i] = gb[k][i] = 0.f;
   }
 
   for (long long base = warp_first; base < rows; base += warp_step) {
@@ -161,26 +167,32 @@ layernorm_2d_bwd_kernel(uint4* __restrict__ dx, float* __restrict__ part, const 
     const float2 st = valid ? stats[row] : make_float2(0.f, 0.f);
     const uint4* xr = x + row * pieces;
     const uint4* dr = dy + row * pieces;
-    float xh[K][8], g[K][8];
+    // the operands stay packed (fp16) between the two passes to keep the register count low
+    uint4 ux[K], ud[K];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int piece = lane_in_group + k * t;
-      uint4 ux = make_uint4(0u, 0u, 0u, 0u), ud = make_uint4(0u, 0u, 0u, 0u);
+      ux[k] = make_uint4(0u, 0u, 0u, 0u);
+      ud[k] = make_uint4(0u, 0u, 0u, 0u);
       if (valid && piece < pieces) {
-        ux = __ldcs(xr + piece);
-        ud = __ldcs(dr + piece);
+        ux[k] = __ldcs(xr + piece);
+        ud[k] = __ldcs(dr + piece);
       }
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const bool on = valid && lane_in_group + k * t < pieces;
       float xv[8], dv[8];
-      unpack8(ux, xv);
-      unpack8(ud, dv);
+      unpack8(ux[k], xv);
+      unpack8(ud[k], dv);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        xh[k][i] = (valid && piece < pieces) ? (xv[i] - st.x) * st.y : 0.f;
-        g[k][i] = dv[i] * w[k][i];
-        s1 += g[k][i];
-        s2 += g[k][i] * xh[k][i];
-        gw[k][i] += dv[i] * xh[k][i];
+        const float xh = on ? (xv[i] - st.x) * st.y : 0.f;
+        const float g = dv[i] * w[k][i];
+        s1 += g;
+        s2 += g * xh;
+        gw[k][i] += dv[i] * xh;
         gb[k][i] += dv[i];
       }
     }
@@ -191,9 +203,14 @@ layernorm_2d_bwd_kernel(uint4* __restrict__ dx, float* __restrict__ part, const 
     for (int k = 0; k < K; ++k) {
       const int piece = lane_in_group + k * t;
       if (valid && piece < pieces) {
-        float o[8];
+        float xv[8], dv[8], o[8];
+        unpack8(ux[k], xv);
+        unpack8(ud[k], dv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = st.y * (g[k][i] - s1 - xh[k][i] * s2);
+        for (int i = 0; i < 8; ++i) {
+          const float xh = (xv[i] - st.x) * st.y;
+          o[i] = st.y * (dv[i] * w[k][i] - s1 - xh * s2);
+        }
         or_[piece] = pack8(o);
       }
     }
@@ -269,7 +286,7 @@ int ln_plan(long long rows, int c, LnPlan* p) {
     return jit_fail("CUDA error: no device");
   const long long groups_per_cta = kLnThreads / t;
   long long want = (rows + groups_per_cta - 1) / groups_per_cta;
-  const long long cap = (long long)sms * 8;  // 8 resident CTAs of 256 threads per SM
+  const long long cap = (long long)sms * 4;  // a few CTAs per SM: weights are loaded once per thread
   p->grid = (int)(want < cap ? want : cap);
   return 0;
 }
