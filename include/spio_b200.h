@@ -138,6 +138,15 @@ int spio_conv2d_gw8_dgrad_host(void* dx, const void* dy, const void* w,
 int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy,
                                const spio_gw8_shape* shape, const spio_gw8_tune* tune);
 
+/* One training step of a layer on host buffers: y = fprop(x, w, bias), dx = dgrad(dy, w),
+ * dw = wgrad(x, dy) and, if dbias is not NULL (odd number of taps only), dbias.  x and dy are
+ * uploaded once, in 16 pieces of the batch; fprop and dgrad of a piece run while the next piece
+ * uploads and the previous one's y and dx download, so the call costs about one upload of x and
+ * dy instead of the four uploads and two downloads of the three separate calls.  Pinned host
+ * memory is needed for the copies to overlap.  Returns after all results are in host memory. */
+int spio_conv2d_gw8_step_host(void* y, void* dx, float* dw, float* dbias, const void* x, const void* dy,
+                              const void* w, const float* bias, const spio_gw8_shape* shape);
+
 /* Reports the launch the library would make; kind is SPIO_GW8_FPROP/DGRAD/WGRAD.
  * Needs a CUDA device (it reads the SM count and the shared-memory limit). */
 int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,

@@ -81,6 +81,8 @@ SIGNATURES = {
         c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune)]),
     "spio_conv2d_gw8_wgrad_host": (
         c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune)]),
+    "spio_conv2d_gw8_step_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape)]),
     "spio_conv2d_gw8_plan": (c_int, [c_int, POINTER(Shape), POINTER(Tune), POINTER(PlanInfo)]),
     "spio_conv2d_gw8_plan_for": (
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),

@@ -532,10 +532,17 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
 
 // ---------------------------------------------------------------- host-buffer variants
 
+constexpr int kStageBuffers = 9;
+constexpr int kStepChunks = 16;  // pieces of the batch the pipelined step call works in
+
 struct HostStage {
   cudaStream_t stream = nullptr;
-  void* buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
-  size_t cap[5] = {0, 0, 0, 0, 0};
+  // the pipelined step call: upload, compute and download streams, one event pair per piece
+  cudaStream_t up = nullptr, down = nullptr;
+  cudaEvent_t uploaded[kStepChunks] = {}, computed[kStepChunks + 1] = {};
+  bool step_ready = false;
+  void* buf[kStageBuffers] = {};
+  size_t cap[kStageBuffers] = {};
 };
 HostStage g_stage[kMaxDevices];
 std::mutex g_stage_mutex;
@@ -696,6 +703,75 @@ int spio_conv2d_gw8_fprop_host(void* y, const void* x, const void* w, const floa
                  bias ? (const float*)st->buf[3] : nullptr, shape, tune, st->stream))
     return 1;
   GW8_CUDA(cudaMemcpyAsync(y, st->buf[1], yb, cudaMemcpyDeviceToHost, st->stream));
+  GW8_CUDA(cudaStreamSynchronize(st->stream));
+  return 0;
+}
+
+int spio_conv2d_gw8_step_host(void* y, void* dx, float* dw, float* dbias, const void* x, const void* dy,
+                              const void* w, const float* bias, const spio_gw8_shape* shape) {
+  if (check_shape(shape)) return 1;
+  if (y == nullptr || dx == nullptr || dw == nullptr || x == nullptr || dy == nullptr || w == nullptr)
+    return fail("NULL host pointer");
+  if (dbias != nullptr && (shape->r * shape->s) % 2 == 0)
+    return fail("the fused bias gradient needs an odd number of filter taps (r * s)");
+  std::lock_guard<std::mutex> lock(g_stage_mutex);
+  HostStage* st = nullptr;
+  if (get_stage(&st)) return 1;
+  if (!st->step_ready) {
+    GW8_CUDA(cudaStreamCreateWithFlags(&st->up, cudaStreamNonBlocking));
+    GW8_CUDA(cudaStreamCreateWithFlags(&st->down, cudaStreamNonBlocking));
+    for (int i = 0; i < kStepChunks; ++i) GW8_CUDA(cudaEventCreateWithFlags(&st->uploaded[i], cudaEventDisableTiming));
+    for (int i = 0; i <= kStepChunks; ++i) GW8_CUDA(cudaEventCreateWithFlags(&st->computed[i], cudaEventDisableTiming));
+    st->step_ready = true;
+  }
+  const size_t xb = act_bytes(shape, false), yb = act_bytes(shape, true);
+  const size_t wb = weight_elems(shape) * 2, dwb = weight_elems(shape) * 4, bb = (size_t)shape->c * 4;
+  const size_t scratch = spio_conv2d_gw8_wgrad_scratch_bytes(shape, nullptr);
+  if (scratch == 0) return 1;
+  // device copies of x, dy (whole batch: the weight gradient needs all of it), y, dx, w, bias, dw, dbias, scratch
+  if (stage_reserve(*st, 0, xb) || stage_reserve(*st, 1, yb) || stage_reserve(*st, 2, wb) ||
+      stage_reserve(*st, 3, bb) || stage_reserve(*st, 4, scratch) || stage_reserve(*st, 5, yb) ||
+      stage_reserve(*st, 6, xb) || stage_reserve(*st, 7, dwb) || stage_reserve(*st, 8, bb))
+    return 1;
+  char* d_x = static_cast<char*>(st->buf[0]);
+  char* d_dy = static_cast<char*>(st->buf[1]);
+  char* d_y = static_cast<char*>(st->buf[5]);
+  char* d_dx = static_cast<char*>(st->buf[6]);
+  const float* d_bias = bias ? static_cast<const float*>(st->buf[3]) : nullptr;
+  GW8_CUDA(cudaMemcpyAsync(st->buf[2], w, wb, cudaMemcpyHostToDevice, st->up));
+  if (bias) GW8_CUDA(cudaMemcpyAsync(st->buf[3], bias, bb, cudaMemcpyHostToDevice, st->up));
+  const int n = shape->n;
+  const int pieces = n < kStepChunks ? n : kStepChunks;
+  const size_t x_img = xb / (size_t)n, y_img = yb / (size_t)n;
+  // Piece i: upload its images of x and dy; as soon as they are there, fprop and dgrad run on
+  // them; as soon as those are done, y and dx of the piece go back.  The three streams overlap,
+  // so the step costs about one upload of x and dy.
+  for (int i = 0; i < pieces; ++i) {
+    const int n0 = (int)((long long)n * i / pieces), n1 = (int)((long long)n * (i + 1) / pieces);
+    const size_t xo = x_img * (size_t)n0, yo = y_img * (size_t)n0;
+    const size_t xs = x_img * (size_t)(n1 - n0), ys = y_img * (size_t)(n1 - n0);
+    GW8_CUDA(cudaMemcpyAsync(d_x + xo, static_cast<const char*>(x) + xo, xs, cudaMemcpyHostToDevice, st->up));
+    GW8_CUDA(cudaMemcpyAsync(d_dy + yo, static_cast<const char*>(dy) + yo, ys, cudaMemcpyHostToDevice, st->up));
+    GW8_CUDA(cudaEventRecord(st->uploaded[i], st->up));
+    GW8_CUDA(cudaStreamWaitEvent(st->stream, st->uploaded[i], 0));
+    spio_gw8_shape part = *shape;
+    part.n = n1 - n0;
+    if (launch_fwd(SPIO_GW8_FPROP, d_y + yo, d_x + xo, st->buf[2], d_bias, &part, nullptr, st->stream)) return 1;
+    if (launch_fwd(SPIO_GW8_DGRAD, d_dx + xo, d_dy + yo, st->buf[2], nullptr, &part, nullptr, st->stream)) return 1;
+    GW8_CUDA(cudaEventRecord(st->computed[i], st->stream));
+    GW8_CUDA(cudaStreamWaitEvent(st->down, st->computed[i], 0));
+    GW8_CUDA(cudaMemcpyAsync(static_cast<char*>(y) + yo, d_y + yo, ys, cudaMemcpyDeviceToHost, st->down));
+    GW8_CUDA(cudaMemcpyAsync(static_cast<char*>(dx) + xo, d_dx + xo, xs, cudaMemcpyDeviceToHost, st->down));
+  }
+  // the weight (and bias) gradient over the whole batch, now resident on the device
+  if (launch_wgrad(static_cast<float*>(st->buf[7]), d_x, d_dy, shape, nullptr, st->buf[4], scratch, st->stream,
+                   L2_HINT_NONE, L2_HINT_NONE, dbias ? static_cast<float*>(st->buf[8]) : nullptr))
+    return 1;
+  GW8_CUDA(cudaEventRecord(st->computed[kStepChunks], st->stream));
+  GW8_CUDA(cudaStreamWaitEvent(st->down, st->computed[kStepChunks], 0));
+  GW8_CUDA(cudaMemcpyAsync(dw, st->buf[7], dwb, cudaMemcpyDeviceToHost, st->down));
+  if (dbias) GW8_CUDA(cudaMemcpyAsync(dbias, st->buf[8], bb, cudaMemcpyDeviceToHost, st->down));
+  GW8_CUDA(cudaStreamSynchronize(st->down));
   GW8_CUDA(cudaStreamSynchronize(st->stream));
   return 0;
 }

@@ -107,3 +107,37 @@ def test_fused_bias_gradient_rejects_even_taps():
     xd, wd, dyd = (capi.to_dev(t) for t in (x, w, dy))
     with pytest.raises(ValueError, match="odd number of filter taps"):
         capi.backward(xd, dyd, wd, sh, with_bias=True)
+
+
+def test_step_host_matches_the_device_entry_points():
+    """The pipelined host-buffer step (uploads, kernels and downloads of 16 pieces of the batch
+    overlapping) returns bit for bit what the device-pointer entry points compute."""
+    import ctypes
+
+    from spio_b200 import _clib
+
+    lib = _clib.load()
+    for sh, with_bias in ((O.Shape(37, 64, 56, 56, 3, 3, 1, 1), True), (O.Shape(5, 72, 9, 20, 3, 3, 1, 1), False),
+                          (O.Shape(40, 128, 14, 14, 5, 5, 2, 2), True)):
+        x, w, b, dy = O.make_inputs(sh, seed=12, bias=with_bias)
+        xd, wd, bd, dyd = (capi.to_dev(t) for t in (x, w, b, dy))
+        hx = x.permute(0, 2, 3, 1).contiguous().pin_memory()
+        hdy = dy.permute(0, 2, 3, 1).contiguous().pin_memory()
+        hw = w.permute(0, 2, 3, 1).contiguous().pin_memory()
+        hb = b.contiguous().pin_memory() if with_bias else None
+        hy = torch.empty(sh.n, sh.p, sh.q, sh.c, dtype=torch.float16).pin_memory()
+        hdx = torch.empty(sh.n, sh.h, sh.w, sh.c, dtype=torch.float16).pin_memory()
+        hdw = torch.empty(sh.c, sh.r, sh.s, 8, dtype=torch.float32).pin_memory()
+        hdb = torch.empty(sh.c, dtype=torch.float32).pin_memory()
+        s = capi.cshape(sh)
+        for _ in range(2):   # the second call reuses the staging buffers and events
+            hy.fill_(-1), hdx.fill_(-1), hdw.fill_(-1)
+            _clib.check(lib.spio_conv2d_gw8_step_host(
+                hy.data_ptr(), hdx.data_ptr(), hdw.data_ptr(), hdb.data_ptr(), hx.data_ptr(), hdy.data_ptr(),
+                hw.data_ptr(), hb.data_ptr() if with_bias else None, ctypes.byref(s)))
+            assert torch.equal(hy, capi.fprop(xd, wd, bd, sh).permute(0, 2, 3, 1).cpu())
+            assert torch.equal(hdx, capi.dgrad(dyd, wd, sh).permute(0, 2, 3, 1).cpu())
+            assert torch.equal(hdw, capi.wgrad(xd, dyd, sh).permute(0, 2, 3, 1).cpu())
+            ref_db = dy.double().sum(dim=(0, 2, 3))
+            assert float((hdb.double() - ref_db).abs().max()) <= 1e-5 * float(dy.double().abs().sum(dim=(0, 2, 3)).max()) + 1e-6
+    assert capi.status() == 0
