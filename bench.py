@@ -343,7 +343,7 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": 2 * act_bytes + C * R * S * 8 * 4,
                     "matches_device_path": e2e_ok,
                     "api": "spio_conv2d_gw8_step_host (pinned host buffers; uploads, kernels and downloads "
-                           "of 16 pieces of the batch overlap on three streams)"},
+                           "of 32 pieces of the batch overlap on three streams)"},
             "gpu_launches": 4 * args.steps,
             "clocks": clocks,
         }

@@ -140,7 +140,7 @@ int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy,
 
 /* One training step of a layer on host buffers: y = fprop(x, w, bias), dx = dgrad(dy, w),
  * dw = wgrad(x, dy) and, if dbias is not NULL (odd number of taps only), dbias.  x and dy are
- * uploaded once, in 16 pieces of the batch; fprop and dgrad of a piece run while the next piece
+ * uploaded once, in 32 pieces of the batch; fprop and dgrad of a piece run while the next piece
  * uploads and the previous one's y and dx download, so the call costs about one upload of x and
  * dy instead of the four uploads and two downloads of the three separate calls.  Pinned host
  * memory is needed for the copies to overlap.  Returns after all results are in host memory. */

@@ -533,7 +533,7 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
 // ---------------------------------------------------------------- host-buffer variants
 
 constexpr int kStageBuffers = 9;
-constexpr int kStepChunks = 16;  // pieces of the batch the pipelined step call works in
+constexpr int kStepChunks = 32;  // pieces of the batch the pipelined step call works in
 
 struct HostStage {
   cudaStream_t stream = nullptr;

@@ -110,7 +110,7 @@ def test_fused_bias_gradient_rejects_even_taps():
 
 
 def test_step_host_matches_the_device_entry_points():
-    """The pipelined host-buffer step (uploads, kernels and downloads of 16 pieces of the batch
+    """The pipelined host-buffer step (uploads, kernels and downloads of 32 pieces of the batch
     overlapping) returns bit for bit what the device-pointer entry points compute."""
     import ctypes
 
