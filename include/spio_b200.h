@@ -185,17 +185,20 @@ int spio_function_launch(void* function, int grid, int block, int smem_bytes, vo
  * and the geometry it takes by value, the launch dimensions and the status word.  Kernel
  * parameter lists:
  *   fprop / dgrad: (in_map, out_map, geom, const half* w, const float* bias, int ns, int nob, int* status)
+ *   fprop / dgrad, engine 2 (tcgen05 kernel, conv2d_gw8_fwd_tc_body<Gw8TcConfig<R, S>>):
+ *                  (in_map, row_map, out_map, geom, const half* w, const float* bias, int ns, int nob, int* status)
  *   wgrad:         (in_map, out_map, geom, float* scratch, int ns, int* status), followed by
  *                  spio_conv2d_gw8_wgrad_reduce(dw, dbias or NULL, scratch, c, r*s, n_parts, stream). */
 typedef struct spio_gw8_launch {
   unsigned long long in_map[16];   /* CUtensorMap of the streamed operand (x; dy for dgrad) */
   unsigned long long out_map[16];  /* CUtensorMap of the tiled operand (y; dx; dy for wgrad) */
+  unsigned long long row_map[16];  /* engine 2 only: the streamed operand with a box of one row */
   int geom[32];                    /* kernel-side geometry struct, opaque */
   int ns, nob, grid, threads, smem_bytes, n_parts;
   size_t scratch_bytes;
   int* status;
 } spio_gw8_launch;
-/* tune->wpg, tpw, pps must be given; they need not be a compiled variant.  plan_jit is the
+/* tune->wpg, tpw, pps must be given (or tune->engine = 2); they need not be a compiled variant.  plan_jit is the
  * host-only planner for such a configuration (cf. spio_conv2d_gw8_plan_for). */
 int spio_conv2d_gw8_plan_jit(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, int sm_count,
                              int smem_optin_bytes, spio_gw8_plan_info* info);

@@ -26,6 +26,18 @@ extern "C" __global__ void __launch_bounds__(Cfg::THREADS, 1)
 }}
 """
 
+TC_SOURCE = """\
+#include "conv2d_gw8_fwd_tc.cuh"
+using namespace spio_b200;
+using Cfg = Gw8TcConfig<{r}, {s}>;
+extern "C" __global__ void __launch_bounds__(Cfg::THREADS, 1)
+{name}(const __grid_constant__ TensorMap in_map, const __grid_constant__ TensorMap row_map,
+       const __grid_constant__ TensorMap out_map, const Gw8Geom g, const __half* __restrict__ wgt,
+       const float* __restrict__ bias, int ns, int nob, int* __restrict__ status) {{
+  conv2d_gw8_fwd_tc_body<Cfg>(in_map, row_map, out_map, g, wgt, bias, ns, nob, status);
+}}
+"""
+
 WGRAD_SOURCE = """\
 #include "conv2d_gw8_wgrad.cuh"
 using namespace spio_b200;
@@ -38,7 +50,8 @@ extern "C" __global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
 """
 
 
-def kernel_source(kernel_name: str, wgrad: bool, r: int, s: int, wpg: int, tpw: int, pps: int) -> str:
+def kernel_source(kernel_name: str, wgrad: bool, r: int, s: int, wpg: int, tpw: int, pps: int,
+                  engine: int = 1) -> str:
     """Source text of the translation unit for one kernel.
 
     ``tpw`` counts 8-pixel tiles per warp.  The weight-gradient kernel is instantiated
@@ -47,6 +60,10 @@ def kernel_source(kernel_name: str, wgrad: bool, r: int, s: int, wpg: int, tpw: 
     """
     if not kernel_name.isidentifier():
         raise ValueError(f"{kernel_name!r} is not a valid kernel name")
+    if engine == 2:
+        if wgrad or r > 3 or s > 3:
+            raise ValueError("the tcgen05 kernel computes fprop and dgrad for filters up to 3 x 3")
+        return TC_SOURCE.format(name=kernel_name, r=r, s=s)
     if wgrad:
         return WGRAD_SOURCE.format(name=kernel_name, r=r, s=s, wpg=wpg, tiles=tpw, pps=pps)
     return FORWARD_SOURCE.format(name=kernel_name, r=r, s=s, wpg=wpg, tiles=(tpw + 1) // 2, pps=pps)

@@ -835,10 +835,14 @@ int spio_conv2d_gw8_plan_jit(int kind, const spio_gw8_shape* shape, const spio_g
                              int smem_optin_bytes, spio_gw8_plan_info* info) {
   if (info == nullptr) return fail("info is NULL");
   if (sm_count <= 0 || smem_optin_bytes <= 0) return fail("sm_count and smem_optin_bytes must be positive");
-  Gw8Variant v;
-  if (jit_variant(kind, shape, tune, &v)) return 1;
   Plan pl;
-  if (make_plan(kind, shape, tune, sm_count, smem_optin_bytes, g_variants, &pl, &v)) return 1;
+  if (tune != nullptr && tune->engine == 2) {  // the tcgen05 kernel has one configuration per filter size
+    if (make_plan(kind, shape, tune, sm_count, smem_optin_bytes, g_variants, &pl)) return 1;
+  } else {
+    Gw8Variant v;
+    if (jit_variant(kind, shape, tune, &v)) return 1;
+    if (make_plan(kind, shape, tune, sm_count, smem_optin_bytes, g_variants, &pl, &v)) return 1;
+  }
   fill_info(pl, info);
   return 0;
 }
@@ -849,18 +853,27 @@ int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const 
   static_assert(sizeof(CUtensorMap) == sizeof(out->in_map), "tensor map size");
   if (out == nullptr) return fail("NULL argument");
   if (streamed == nullptr || tiled == nullptr) return fail("NULL tensor pointer");
-  Gw8Variant v;
-  if (jit_variant(kind, shape, tune, &v)) return 1;
   const DeviceInfo* d = nullptr;
   if (device_info(&d)) return 1;
   Plan pl;
-  if (make_plan(kind, shape, tune, d->sms, d->smem_optin, g_variants, &pl, &v)) return 1;
-  const Gw8Geom& g = pl.g;
+  CUtensorMap a, b, row;
   memset(out, 0, sizeof *out);
-  CUtensorMap a, b;
-  if (encode_map(&a, streamed, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * v.pps, g.nb)) return 1;
-  if (encode_map(&b, tiled, g.c, g.out_w, g.out_h, g.n, g.wt, kind == SPIO_GW8_WGRAD ? 2 * v.pps : 2, g.nb))
-    return 1;
+  if (tune != nullptr && tune->engine == 2) {
+    if (make_plan(kind, shape, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
+    if (encode_map(&a, streamed, pl.g.c, pl.g.in_w, pl.g.in_h, pl.g.n, 64, 2, 1)) return 1;
+    if (encode_map(&row, streamed, pl.g.c, pl.g.in_w, pl.g.in_h, pl.g.n, 64, 1, 1)) return 1;
+    if (encode_map(&b, tiled, pl.g.c, pl.g.out_w, pl.g.out_h, pl.g.n, pl.g.wt, 2, 1)) return 1;
+    memcpy(out->row_map, &row, sizeof row);
+  } else {
+    Gw8Variant v;
+    if (jit_variant(kind, shape, tune, &v)) return 1;
+    if (make_plan(kind, shape, tune, d->sms, d->smem_optin, g_variants, &pl, &v)) return 1;
+    if (encode_map(&a, streamed, pl.g.c, pl.g.in_w, pl.g.in_h, pl.g.n, pl.g.bw, 2 * v.pps, pl.g.nb)) return 1;
+    if (encode_map(&b, tiled, pl.g.c, pl.g.out_w, pl.g.out_h, pl.g.n, pl.g.wt,
+                   kind == SPIO_GW8_WGRAD ? 2 * v.pps : 2, pl.g.nb))
+      return 1;
+  }
+  const Gw8Geom& g = pl.g;
   memcpy(out->in_map, &a, sizeof a);
   memcpy(out->out_map, &b, sizeof b);
   memcpy(out->geom, &g, sizeof g);

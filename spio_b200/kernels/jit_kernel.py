@@ -34,7 +34,7 @@ class JitKernel(Kernel):
     def _resolve_tune(self, attr) -> None:
         """Fill wpg / tpw / pps from the launch planner when the configuration leaves them open."""
         t = self._tune
-        if t is not None and t.wpg > 0 and t.tpw > 0 and t.pps > 0:
+        if t is not None and (t.engine == 2 or (t.wpg > 0 and t.tpw > 0 and t.pps > 0)):
             return
         info = _clib.PlanInfo()
         _clib.check(_clib.load().spio_conv2d_gw8_plan_for(
@@ -47,6 +47,8 @@ class JitKernel(Kernel):
     @property
     def function_name(self) -> str:
         t = self._tune
+        if t.engine == 2:
+            return f"{self.kernel_name}__tcgen05"
         return f"{self.kernel_name}__wpg{t.wpg}_tpw{t.tpw}_pps{t.pps}"
 
     @property
@@ -55,7 +57,7 @@ class JitKernel(Kernel):
 
         t = self._tune
         return kernel_source(self.function_name, self.kind == _clib.WGRAD, self.params.r, self.params.s,
-                             t.wpg, t.tpw, t.pps)
+                             t.wpg, t.tpw, t.pps, engine=2 if t.engine == 2 else 1)
 
     def compile(self, device_attr=None) -> None:
         from ..compiler import flags
@@ -129,7 +131,8 @@ class JitKernel(Kernel):
                 else:
                     if args[2].data_ptr() % 16:
                         raise ValueError("weight pointer must be 16-byte aligned")
-                    kargs = [lp.in_map, lp.out_map, lp.geom, args[2], args[3], int(lp.ns), int(lp.nob), status]
+                    maps = [lp.in_map, lp.row_map, lp.out_map] if self._tune.engine == 2 else [lp.in_map, lp.out_map]
+                    kargs = maps + [lp.geom, args[2], args[3], int(lp.ns), int(lp.nob), status]
                 self.function.launch(lp.grid, lp.threads, kargs, shared_mem_bytes=lp.smem_bytes, stream=stream)
                 if self.kind == _clib.WGRAD:
                     _clib.check(self._lib.spio_conv2d_gw8_wgrad_reduce(

@@ -18,10 +18,10 @@ def _wants_jit(params, config) -> bool:
     from ..compiler import flags
 
     tune = config.as_tune() if config is not None else {}
-    if tune.get("engine", 0) == 2:
-        return False  # the tcgen05 kernel is built into the library only
     if flags.jit.get():
         return True
+    if tune.get("engine", 0) == 2:
+        return False  # built into the library for every filter size it supports
     wpg, tpw, pps = (tune.get(k, 0) for k in ("wpg", "tpw", "pps"))
     if not (wpg and tpw and pps):
         return False

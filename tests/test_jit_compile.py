@@ -145,3 +145,18 @@ def test_module_load_needs_a_device():
 
     with pytest.raises(ValueError, match="CUDA error"):
         Module().load_data(b"\x7fELF")
+
+
+def test_tcgen05_kernel_compiles_just_in_time():
+    """The tcgen05 / tensor-memory forward kernel goes through NVRTC like the others."""
+    p = Conv2dGw8Params(n=8, c=128, h=28, w=40, r=3, s=3, padding=1)
+    k = conv2d_gw8_kernel_factory.make_kernel(p, Conv2dGw8Config(engine=2), jit=True, igrad=True)
+    assert isinstance(k, JitKernel)
+    k.compile(B200_ATTRIBUTES)
+    assert k.cubin[:4] == ELF_MAGIC and k.function_name.endswith("__tcgen05")
+    assert k.plan["engine"] == 2 and k.plan["threads"] == 640
+    assert "tcgen05" in k.source and "Gw8TcConfig<3, 3>" in k.source
+    built_in = conv2d_gw8_kernel_factory.make_kernel(p, Conv2dGw8Config(engine=2))
+    assert type(built_in) is Kernel
+    with pytest.raises(ValueError):
+        kernel_source("k", True, 3, 3, 0, 0, 1, engine=2)

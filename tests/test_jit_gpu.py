@@ -145,3 +145,23 @@ def test_functional_path_with_jit_flag():
     O.assert_close(y.detach(), O.c_fprop(x, w, b, sh), sh, "fprop", "jit functional")
     O.assert_close(xd.grad, O.c_dgrad(dy, w, sh), sh, "dgrad", "jit functional")
     O.assert_close(wd.grad.float(), O.c_wgrad(x, dy, sh), sh, "wgrad", "jit functional", 2.0)
+
+
+def test_jit_tcgen05_kernel_is_bit_identical_to_the_built_in_one():
+    sh = O.Shape(6, 136, 30, 56, 3, 3, 1, 1)
+    x, w, b, dy = O.make_inputs(sh, seed=13, bias=True)
+    xd, wd, bd, dyd = (capi.to_dev(t) for t in (x, w, b, dy))
+    p = params_of(sh, has_bias=True)
+    cfg = Conv2dGw8Config(engine=2)
+    out = []
+    for jit in (False, True):
+        y = dead((sh.n, sh.c, sh.p, sh.q), torch.float16)
+        k = run(conv2d_gw8_kernel_factory, p, cfg, (y, xd, wd, bd), jit=jit)
+        assert isinstance(k, JitKernel) == jit
+        dx = dead((sh.n, sh.c, sh.h, sh.w), torch.float16)
+        run(conv2d_gw8_kernel_factory, p, cfg, (dx, dyd, wd, None), jit=jit, igrad=True)
+        out.append((y, dx))
+    assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
+    O.assert_close(out[1][0], O.c_fprop(x, w, b, sh), sh, "fprop", "jit tcgen05")
+    O.assert_close(out[1][1], O.c_dgrad(dy, w, sh), sh, "dgrad", "jit tcgen05")
+    assert capi.status() == 0
