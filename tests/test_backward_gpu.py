@@ -141,3 +141,39 @@ def test_step_host_matches_the_device_entry_points():
             ref_db = dy.double().sum(dim=(0, 2, 3))
             assert float((hdb.double() - ref_db).abs().max()) <= 1e-5 * float(dy.double().abs().sum(dim=(0, 2, 3)).max()) + 1e-6
     assert capi.status() == 0
+
+
+def test_step_is_capturable_in_a_cuda_graph():
+    """fprop + the combined backward call (programmatic dependent launches, event record)
+    captured into a CUDA graph and replayed give the results of the eager calls."""
+    import ctypes
+
+    from spio_b200 import _clib
+
+    lib = _clib.load()
+    sh = O.Shape(24, 64, 56, 56, 3, 3, 1, 1)
+    x, w, b, dy = O.make_inputs(sh, seed=6, bias=True)
+    xd, wd, bd, dyd = (capi.to_dev(t) for t in (x, w, b, dy))
+    ref_y, ref_dx, ref_dw = capi.fprop(xd, wd, bd, sh), capi.dgrad(dyd, wd, sh), capi.wgrad(xd, dyd, sh)
+    s = capi.cshape(sh)
+    y, dx = torch.empty_like(ref_y), torch.empty_like(ref_dx)
+    dw = torch.empty_like(ref_dw)
+    db = torch.empty(sh.c, dtype=torch.float32, device="cuda")
+    nbytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(ctypes.byref(s), None)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph, stream=side):
+        sp = side.cuda_stream
+        _clib.check(lib.spio_conv2d_gw8_fprop(y.data_ptr(), xd.data_ptr(), wd.data_ptr(), bd.data_ptr(),
+                                              ctypes.byref(s), None, sp))
+        _clib.check(lib.spio_conv2d_gw8_backward(dx.data_ptr(), dw.data_ptr(), db.data_ptr(), xd.data_ptr(),
+                                                 dyd.data_ptr(), wd.data_ptr(), ctypes.byref(s), None, None,
+                                                 scratch.data_ptr(), nbytes, sp, None))
+    for _ in range(3):
+        y.fill_(-1), dx.fill_(-1), dw.fill_(-1)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, ref_y) and torch.equal(dx, ref_dx) and torch.equal(dw, ref_dw)
+    assert capi.status() == 0
