@@ -130,4 +130,6 @@ def main(root: Path) -> None:
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of the andravin/spio checkout>")
+    main(Path(sys.argv[1]))
