@@ -94,6 +94,8 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   };
 
   if (warp >= NCW) {
+    // the producer warpgroup keeps 24 registers per thread and frees the rest for the consumers
+    if (Cfg::FWD_SETMAXNREG) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::FWD_REGS_PRODUCER));
     const int total = g.n_chunks * g.n_ig * g.n_ct * g.n_pairs;
     const int u0 = gw8_span_begin(total, blockIdx.x, gridDim.x);
     const int u1 = gw8_span_begin(total, blockIdx.x + 1, gridDim.x);
@@ -136,7 +138,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
           mbar_arrive(full(slot));
         }
       }
-    } else {
+    } else if (warp == NCW + 1) {
       // ---------------------------------------------------------- store warp
       // Lane i owns staging buffer i: it waits until the compute warps have filled it,
       // issues the TMA stores of the stage and releases the buffer once they have read
@@ -181,6 +183,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
       }
     }
   } else {
+    if (Cfg::FWD_SETMAXNREG) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::FWD_REGS_CONSUMER));
     // ------------------------------------------------------------ compute warps
     // A warp owns one channel group and TPW "block tiles": 16 consecutive pixels of the
     // rows of one image.  For each input row and each pair of column shifts (s, s+1) ONE

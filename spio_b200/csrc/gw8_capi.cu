@@ -126,6 +126,21 @@ int device_info(const DeviceInfo** out) {
         GW8_CUDA(cudaFuncSetAttribute(gw8_tc_kernel(r, sft), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       d.smem_optin - kTcStaticSmem));
     for (const Gw8Variant& v : g_variants) {
+      // Forward kernels that move registers from the producer warpgroup to the consumers
+      // (setmaxnreg) must have been allocated the count the move was sized for; otherwise the
+      // consumers could wait for registers that never become free.
+      if (v.wpg >= 2) {
+        cudaFuncAttributes fa;
+        GW8_CUDA(cudaFuncGetAttributes(&fa, v.fwd_kernel));
+        const int launch = fa.numRegs, consumer = v.wpg == 2 ? 112 : 80;
+        if (launch > consumer || 8 * v.wpg * 32 * (consumer - launch) > 128 * (launch - 24)) {
+          char buf[160];
+          snprintf(buf, sizeof buf,
+                   "forward kernel r%d s%d wpg%d tpw%d pps%d was allocated %d registers per thread; "
+                   "its register hand-over does not fit", v.r, v.s, v.wpg, v.tpw, v.pps, launch);
+          return fail(buf);
+        }
+      }
       GW8_CUDA(cudaFuncSetAttribute(v.fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     d.smem_optin - kFwdStaticSmem));
       GW8_CUDA(cudaFuncSetAttribute(v.wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -826,7 +841,7 @@ static int jit_variant(int kind, const spio_gw8_shape* shape, const spio_gw8_tun
   if (check_shape(shape)) return 1;
   *v = Gw8Variant{};
   v->r = shape->r, v->s = shape->s, v->wpg = tune->wpg, v->tpw = tune->tpw, v->pps = tune->pps;
-  v->fwd_threads = (8 * tune->wpg + 2) * 32;
+  v->fwd_threads = (8 * tune->wpg + 4) * 32;
   v->wgrad_threads = (8 * tune->wpg + 1) * 32;
   return 0;
 }

@@ -88,7 +88,23 @@ struct Gw8Config {
   static constexpr int WIN = 2 * E + 2;    // rows of the register window
   static constexpr int NT = R * S;         // taps
   static constexpr int NCW = 8 * WPG;      // consumer warps
-  static constexpr int THREADS = (NCW + 2) * 32;  // + load warp + store warp
+  // Forward kernel: the consumer warps plus one warpgroup (4 warps) of producers: load warp,
+  // store warp and two idle warps.  The padding makes the producers a warpgroup of their own,
+  // so they can hand most of their registers to the consumers (setmaxnreg): the CTA is launched
+  // with FWD_REGS_LAUNCH registers per thread (what ptxas allocates under the launch bound when
+  // the kernel contains setmaxnreg), the producers drop to FWD_REGS_PRODUCER and the consumers
+  // rise to FWD_REGS_CONSUMER.  The rise must fit what the drop frees,
+  //   NCW*32 * (CONSUMER - LAUNCH) <= 128 * (LAUNCH - PRODUCER),
+  // or the consumers would wait for registers for ever; the library checks the allocated count
+  // of every loaded kernel against this before it launches it.
+  static constexpr int THREADS = (NCW + 4) * 32;
+  static constexpr bool FWD_SETMAXNREG = WPG >= 2;  // one warp per group has registers to spare
+  static constexpr int FWD_REGS_LAUNCH = WPG == 2 ? 96 : 72;
+  static constexpr int FWD_REGS_PRODUCER = 24;
+  static constexpr int FWD_REGS_CONSUMER = WPG == 2 ? 112 : 80;
+  static_assert(!FWD_SETMAXNREG ||
+                    NCW * 32 * (FWD_REGS_CONSUMER - FWD_REGS_LAUNCH) <= 128 * (FWD_REGS_LAUNCH - FWD_REGS_PRODUCER),
+                "the consumers' extra registers must fit what the producers give up");
   static constexpr int MAX_TILES = WPG * TPW;
   static constexpr int WGRAD_THREADS = (NCW + 1) * 32;  // no store warp
 };

@@ -89,10 +89,26 @@ class JitKernel(Kernel):
         self._lib = _clib.load()
         self._device_ordinal = device_ordinal
         self.module, self.function = load_kernel(self.function_name, self.cubin, device_ordinal)
+        self._check_register_hand_over()
         self.function.set_max_dynamic_shared_memory_size(self.plan["smem_bytes"])
         self._scratch_bytes = int(self.plan["scratch_bytes"])
         if clear_cubin:
             self.cubin = None
+
+    def _check_register_hand_over(self) -> None:
+        """Forward kernels with two or three warps per group move registers from the producer
+        warpgroup to the consumers (setmaxnreg); the move is sized for the register count ptxas
+        allocates under the kernel's launch bound.  Refuse to launch a kernel that was allocated
+        anything else: its consumers could wait for registers for ever."""
+        t = self._tune
+        if self.kind == _clib.WGRAD or t.engine == 2 or t.wpg < 2:
+            return
+        launch = self.function.get_attribute("num_regs")
+        consumer = 112 if t.wpg == 2 else 80
+        if launch > consumer or 8 * t.wpg * 32 * (consumer - launch) > 128 * (launch - 24):
+            self.unload()
+            raise ValueError(f"Error in kernel {self}: allocated {launch} registers per thread; "
+                             f"the register hand-over of the forward kernel does not fit")
 
     def unload(self) -> None:
         self.function = None

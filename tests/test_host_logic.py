@@ -111,7 +111,7 @@ def test_kernel_names_and_compile_without_device():
     assert conv2d_gw8_wgrad_kernel_factory.get_kernel_name() == "spio_conv2d_gw8_wgrad"
     k = f.make_kernel(p, Conv2dGw8Config(wpg=2, tpw=2, pps=1), B200_ATTRIBUTES)
     k.compile(B200_ATTRIBUTES)
-    assert k.plan["wpg"] == 2 and k.plan["tpw"] == 2 and k.launch_params.block == 576
+    assert k.plan["wpg"] == 2 and k.plan["tpw"] == 2 and k.launch_params.block == 640
     bad = f.make_kernel(p, Conv2dGw8Config(wpg=5), B200_ATTRIBUTES)
     with pytest.raises(ValueError, match="variant"):
         bad.compile(B200_ATTRIBUTES)

@@ -99,7 +99,7 @@ def test_jit_kernel_compile_plans_and_names():
     assert k.cubin[:4] == ELF_MAGIC
     assert k.function_name == f"spio_conv2d_gw8_dgrad__{p.encode()}__wpg1_tpw3_pps1"
     assert k.function_name.encode() in k.cubin
-    assert k.plan["threads"] == (8 * 1 + 2) * 32 and k.plan["wpg"] == 1 and k.plan["tpw"] == 3
+    assert k.plan["threads"] == (8 * 1 + 4) * 32 and k.plan["wpg"] == 1 and k.plan["tpw"] == 3
     assert "registers" in k.compile_log
     lp = k.launch_params
     assert lp.grid >= 1 and lp.block == k.plan["threads"]
