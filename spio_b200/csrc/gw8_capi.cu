@@ -276,9 +276,10 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
     return make_plan_tc(kind, sh, t, sms, smem_optin, p, q, plan);
   }
 
-  // Unless the caller asks otherwise, the forward kernel streams one row pair per slot
-  // (its register window then fits without spills) and the weight-gradient kernel two.
-  const int default_pps = kind == SPIO_GW8_WGRAD ? 2 : 1;
+  // Unless the caller asks otherwise, both kernels stream two row pairs per slot: half the
+  // barrier hand-offs per byte (the forward kernel fits that without spills since its compute
+  // warps take over registers of the producer warpgroup).
+  const int default_pps = 2;
   const Gw8Variant* v = forced;
   for (int pass = 0; pass < 2 && v == nullptr; ++pass) {
     for (const Gw8Variant& cand : variants) {
