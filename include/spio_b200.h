@@ -42,7 +42,7 @@ typedef struct spio_gw8_tune {
   int ncb;   /* 8-pixel column blocks per column tile */
   int nb;    /* images per ring slot */
   int grid;  /* CTAs; 0 = one per SM */
-  int pps;   /* row pairs per ring slot: 1 or 2 */
+  int pps;   /* row pairs per ring slot: 1 or 2 (built-in variants), up to 4 just in time */
   int engine; /* 0 = the planner chooses; 1 = warp-level mma.sync kernels; 2 = tcgen05 kernel with the
                  accumulators in tensor memory (fprop and dgrad, filters up to 3 x 3; it ignores
                  wpg, tpw, nb and pps) */

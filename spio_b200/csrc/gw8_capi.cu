@@ -837,8 +837,8 @@ int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy, const s
 static int jit_variant(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, Gw8Variant* v) {
   if (tune == nullptr) return fail("a just-in-time kernel needs a tile configuration");
   if (kind < SPIO_GW8_FPROP || kind > SPIO_GW8_WGRAD) return fail("unknown kind");
-  if (tune->wpg < 1 || tune->wpg > 3 || tune->tpw < 1 || tune->tpw > 8 || tune->pps < 1 || tune->pps > 2)
-    return fail("a just-in-time kernel needs explicit wpg (1..3), tpw (1..8) and pps (1..2)");
+  if (tune->wpg < 1 || tune->wpg > 3 || tune->tpw < 1 || tune->tpw > 8 || tune->pps < 1 || tune->pps > 4)
+    return fail("a just-in-time kernel needs explicit wpg (1..3), tpw (1..8) and pps (1..4)");
   if (check_shape(shape)) return 1;
   *v = Gw8Variant{};
   v->r = shape->r, v->s = shape->s, v->wpg = tune->wpg, v->tpw = tune->tpw, v->pps = tune->pps;

@@ -117,7 +117,7 @@ def test_plan_jit_rejects_what_cannot_run():
     lib = _clib.load()
     sh = _clib.Shape(4, 64, 32, 32, 3, 3, 1, 1)
     info = _clib.PlanInfo()
-    for tune in ({"wpg": 4, "tpw": 2, "pps": 1}, {"wpg": 2, "tpw": 0, "pps": 1}, {"wpg": 2, "tpw": 2, "pps": 3}):
+    for tune in ({"wpg": 4, "tpw": 2, "pps": 1}, {"wpg": 2, "tpw": 0, "pps": 1}, {"wpg": 2, "tpw": 2, "pps": 5}):
         t = _clib.make_tune(tune)
         assert lib.spio_conv2d_gw8_plan_jit(_clib.FPROP, ctypes.byref(sh), ctypes.byref(t), 148, 232448,
                                             ctypes.byref(info)) != 0
