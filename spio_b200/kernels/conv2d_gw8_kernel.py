@@ -69,7 +69,8 @@ def plan_is_valid(kind: int, params, tune: dict, device_attr) -> bool:
 
 
 def enumerate_tiles(params, out_w: int, wpg: int, tpw: int, forward: bool = False) -> Iterator[tuple]:
-    """(ncb, nb) candidates: the width cut into 1..4 column tiles; several images per slot
+    """(ncb, nb) candidates: (0, 0) = the launch planner's own choice, then the width cut into
+    1..4 column tiles; several images per slot
     only when one tile spans the whole width.  ncb counts 8-pixel column blocks.  The
     weight-gradient kernel holds wpg * tpw tiles of 8 pixels; the forward kernel holds
     wpg * ceil(tpw / 2) blocks of 16 pixels and its column tile is at least 16 pixels wide."""
@@ -77,6 +78,7 @@ def enumerate_tiles(params, out_w: int, wpg: int, tpw: int, forward: bool = Fals
     need = (lambda ncb: divup(max(ncb, 2), 2)) if forward else (lambda ncb: ncb)
     col_blocks = divup(out_w, 8)
     seen = set()
+    yield 0, 0  # always plannable: wide images with few tiles per warp need more column tiles than tried below
     for n_ct in range(1, 5):
         ncb = max(divup(col_blocks, n_ct), 2 if forward else 1)
         if need(ncb) > max_tiles or ncb in seen:

@@ -192,3 +192,18 @@ def test_layernorm_2d_layer_and_op_checks():
     # fake (meta) implementation: shapes and dtypes without a device
     y, stats = torch.ops.spio.layernorm_2d(torch.empty(2, 64, 3, 5, dtype=torch.float16, device="meta"), None, None, 1e-6)
     assert y.shape == (2, 64, 3, 5) and stats.shape == (30, 2) and stats.dtype == torch.float32
+
+
+def test_every_plannable_shape_has_a_configuration():
+    """A wide image with a large filter needs more column tiles than the enumeration tries;
+    the planner's own choice is always part of the configuration space."""
+    from spio_b200.cuda import B200_ATTRIBUTES
+    from spio_b200.kernels import (Conv2dGw8Params, conv2d_gw8_kernel_factory,
+                                   conv2d_gw8_wgrad_kernel_factory)
+
+    for p in (Conv2dGw8Params(n=32, c=64, h=112, w=112, r=5, s=5, padding=2),
+              Conv2dGw8Params(n=2, c=8, h=9, w=300, r=3, s=3, padding=1),
+              Conv2dGw8Params(n=1, c=1024, h=3, w=3, r=1, s=1, padding=0)):
+        assert len(list(conv2d_gw8_kernel_factory.configs(p, B200_ATTRIBUTES))) > 0
+        assert len(list(conv2d_gw8_kernel_factory.configs(p, B200_ATTRIBUTES, igrad=True))) > 0
+        assert len(list(conv2d_gw8_wgrad_kernel_factory.configs(p, B200_ATTRIBUTES))) > 0
