@@ -28,14 +28,16 @@ namespace spio_b200 {
 // inside the CTA through shared memory before the partial is written.  CTAs that walk
 // several chunks (more chunks than CTAs) keep one part per warp instead, n_parts = n_split * WPG.
 //
-// Bias gradient for free: two filter taps share one m16n8k16 (tap 2i in rows 0-7 of A, tap
-// 2i+1 in rows 8-15).  With an odd number of taps the last MMA has rows 8-15 to spare; they
-// are fed ones, so rows 8-15 of its accumulator hold sum over pixels of dy[pixel][k], which
-// is the gradient of the bias.  It is written behind the weight partial of each part.
+// Bias gradient almost for free: two filter taps share one m16n8k16 (tap 2i in rows 0-7 of A,
+// tap 2i+1 in rows 8-15).  With an odd number of taps the last MMA has rows 8-15 to spare; with
+// WITH_BIAS they are fed ones, so rows 8-15 of its accumulator hold sum over pixels of
+// dy[pixel][k], which is the gradient of the bias.  It is written behind the weight partial of
+// each part.  Feeding a register instead of a literal zero costs about 5 % of the kernel's
+// time (measured), so the kernel without it is a separate instantiation.
 #define GW8_PART_FLOATS(taps) (64 * (taps) * 8 + 64)
 // The kernel body is a device function so that both the ahead-of-time instantiations and
 // the just-in-time wrappers (one extern "C" kernel per layer shape) can share it.
-template <class Cfg>
+template <class Cfg, bool WITH_BIAS = false>
 __device__ __forceinline__ void
 conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8Geom& g,
                       float* __restrict__ scratch, int ns, int* __restrict__ status) {
@@ -43,7 +45,7 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
   constexpr int E = Cfg::E, WIN = Cfg::WIN, NT = Cfg::NT, NCW = Cfg::NCW;
   constexpr int NPH = WIN / 2;
   constexpr int NACC = (NT + 1) / 2;
-  constexpr bool BIAS = (NT & 1) != 0;    // the spare half of the last MMA sums dy
+  constexpr bool BIAS = WITH_BIAS && (NT & 1) != 0;  // the spare half of the last MMA sums dy
   constexpr u32 ONES = 0x3C003C00u;       // half2(1, 1)
   constexpr int MAX_NS = 16;
 
@@ -236,7 +238,7 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
                         mma_m16n8k16(acc[k], X[t][pa0][sa], X[t][pb0][sb], X[t][pa1][sa],
                                      X[t][pb1][sb], d0, d1);
                       } else {
-                        mma_m16n8k16(acc[k], X[t][pa0][sa], ONES, X[t][pa1][sa], ONES, d0, d1);
+                        mma_m16n8k16(acc[k], X[t][pa0][sa], BIAS ? ONES : 0u, X[t][pa1][sa], BIAS ? ONES : 0u, d0, d1);
                       }
                     }
                   }
@@ -323,12 +325,12 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
   }
 }
 
-template <class Cfg>
+template <class Cfg, bool WITH_BIAS = false>
 __global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
 conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
                         const __grid_constant__ TensorMap dy_map, const Gw8Geom g,
                         float* __restrict__ scratch, int ns, int* __restrict__ status) {
-  conv2d_gw8_wgrad_body<Cfg>(x_map, dy_map, g, scratch, ns, status);
+  conv2d_gw8_wgrad_body<Cfg, WITH_BIAS>(x_map, dy_map, g, scratch, ns, status);
 }
 
 // dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], and, when dbias

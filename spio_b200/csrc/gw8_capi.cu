@@ -145,6 +145,8 @@ int device_info(const DeviceInfo** out) {
                                     d.smem_optin - kFwdStaticSmem));
       GW8_CUDA(cudaFuncSetAttribute(v.wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     d.smem_optin - kFwdStaticSmem));
+      GW8_CUDA(cudaFuncSetAttribute(v.wgrad_bias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    d.smem_optin - kFwdStaticSmem));
     }
     d.ready = true;
   }
@@ -542,7 +544,8 @@ int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape*
   int ns = pl.ns;
   int* status = d->status;
   void* args[] = {&x_map, &dy_map, (void*)&g, &sc, &ns, &status};
-  if (launch_kernel(pl.v->wgrad_kernel, pl.grid, pl.threads, pl.smem, stream, args)) return 1;
+  const void* kernel = dbias != nullptr ? pl.v->wgrad_bias_kernel : pl.v->wgrad_kernel;
+  if (launch_kernel(kernel, pl.grid, pl.threads, pl.smem, stream, args)) return 1;
   return launch_reduce(dw, dbias, sc, g.c, sh->r * sh->s, pl.n_parts, stream);
 }
 

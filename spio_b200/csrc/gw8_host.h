@@ -28,7 +28,8 @@ struct Gw8Variant {
   int r, s, wpg, tpw, pps;
   int fwd_threads, wgrad_threads;
   const void* fwd_kernel;    // conv2d_gw8_fwd_kernel<Cfg>
-  const void* wgrad_kernel;  // conv2d_gw8_wgrad_kernel<Cfg>
+  const void* wgrad_kernel;       // conv2d_gw8_wgrad_kernel<Cfg, false>
+  const void* wgrad_bias_kernel;  // conv2d_gw8_wgrad_kernel<Cfg, true>: also sums dy for the bias gradient
 };
 
 // Each gw8_inst.cu build (one per filter height R) exports its variants.

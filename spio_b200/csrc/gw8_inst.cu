@@ -24,7 +24,8 @@ Gw8Variant make_variant() {
                     Cfg::THREADS,
                     Cfg::WGRAD_THREADS,
                     (const void*)&conv2d_gw8_fwd_kernel<FwdCfg>,
-                    (const void*)&conv2d_gw8_wgrad_kernel<Cfg>};
+                    (const void*)&conv2d_gw8_wgrad_kernel<Cfg, false>,
+                    (const void*)&conv2d_gw8_wgrad_kernel<Cfg, true>};
 }
 
 // The register window costs WIN * S * TPW registers per thread, so wide or tall
