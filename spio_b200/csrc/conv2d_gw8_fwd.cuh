@@ -67,6 +67,9 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
     mbar_fence_init();
   }
   __syncthreads();
+  // The tensor maps are kernel parameters: fetching them does not depend on earlier kernels.
+  if (threadIdx.x == 32 * NCW) prefetch_tensormap(&in_map);
+  if (threadIdx.x == 32 * (NCW + 1)) prefetch_tensormap(&out_map);
   // Everything above touches only shared memory and may overlap the tail of the preceding
   // kernel.  Dependents are released only after the wait, so a chain of such launches never
   // runs ahead of the work that precedes its first kernel.

@@ -72,6 +72,11 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     mbar_fence_init();
   }
   __syncthreads();
+  // The tensor maps are kernel parameters: fetching them does not depend on earlier kernels.
+  if (threadIdx.x == 32 * NCW) {
+    prefetch_tensormap(&x_map);
+    prefetch_tensormap(&dy_map);
+  }
   // Everything above touches only shared memory and may overlap the tail of the preceding
   // kernel.  Dependents are released only after the wait, so a chain of such launches never
   // runs ahead of the work that precedes its first kernel.
