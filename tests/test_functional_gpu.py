@@ -101,3 +101,37 @@ def test_opcheck():
     kwargs = dict(stride=1, padding_y=1, padding_x=1, dilation=1, groups=sh.groups)
     torch.library.opcheck(torch.ops.spio.conv2d_gw8.default, args, kwargs,
                           test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+
+
+def test_layer_under_torch_compile():
+    """The layer inside a torch.compile'd module (the operator is opaque to the compiler; its
+    fake implementations and autograd registration must hold up) gives the eager results.
+    Mirrors the reference's tests/test_conv2d_gw8.py:227-230."""
+    torch.manual_seed(1)
+    model = Net(64).cuda().to(memory_format=CL)
+    fast, n = _transform(model)
+    assert n == 1
+    x = torch.randn(4, 64, 24, 24, device="cuda").contiguous(memory_format=CL)
+    with torch.autocast("cuda", dtype=torch.float16):
+        eager = fast(x)
+    eager.float().square().mean().backward()
+    eager_grad = fast.conv.weight.grad.clone()
+    fast.zero_grad()
+    compiled = torch.compile(fast)
+    with torch.autocast("cuda", dtype=torch.float16):
+        out = compiled(x)
+    out.float().square().mean().backward()
+    assert device_status() == 0
+    assert torch.allclose(out.float(), eager.float(), rtol=1e-2, atol=1e-2)
+    got = fast.conv.weight.grad
+    assert float((got - eager_grad).abs().max()) <= 1e-2 * float(eager_grad.abs().max()) + 1e-6
+
+
+def test_layernorm_opcheck():
+    from spio_b200.functional import layernorm_2d  # noqa: F401  (registers the operator)
+
+    x = torch.randn(2, 64, 5, 6, device="cuda").half().contiguous(memory_format=CL).requires_grad_(True)
+    w = torch.rand(64, device="cuda").requires_grad_(True)
+    b = torch.rand(64, device="cuda").requires_grad_(True)
+    torch.library.opcheck(torch.ops.spio.layernorm_2d.default, (x, w, b, 1e-6),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
