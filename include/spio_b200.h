@@ -193,7 +193,7 @@ typedef struct spio_gw8_launch {
   unsigned long long in_map[16];   /* CUtensorMap of the streamed operand (x; dy for dgrad) */
   unsigned long long out_map[16];  /* CUtensorMap of the tiled operand (y; dx; dy for wgrad) */
   unsigned long long row_map[16];  /* engine 2 only: the streamed operand with a box of one row */
-  int geom[32];                    /* kernel-side geometry struct, opaque */
+  int geom[40];                    /* kernel-side geometry struct, opaque */
   int ns, nob, grid, threads, smem_bytes, n_parts;
   size_t scratch_bytes;
   int* status;

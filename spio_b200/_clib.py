@@ -52,7 +52,7 @@ class Launch(Structure):
         ("in_map", c_ulonglong * 16),
         ("out_map", c_ulonglong * 16),
         ("row_map", c_ulonglong * 16),
-        ("geom", c_int * 32),
+        ("geom", c_int * 40),
         ("ns", c_int), ("nob", c_int), ("grid", c_int), ("threads", c_int),
         ("smem_bytes", c_int), ("n_parts", c_int),
         ("scratch_bytes", c_size_t),

@@ -44,6 +44,10 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   __shared__ __align__(8) u64 bars[2 * MAX_NS + 2 * MAX_NOB];
   __shared__ Gw8StageDesc desc[MAX_NS];
   __shared__ int abort_flag;
+  constexpr int DYNQ = 32;         // claims in flight between the load lane and the store lanes
+  __shared__ int dynq[DYNQ];       // first unit of every piece the load lane claimed from the pool
+  __shared__ int dyn_count;        // how many it has claimed so far
+  volatile int* const dyn_n = &dyn_count;
 
   // ring slots: [nb][2*PPS rows][bw][64 ch]; staging buffers: PPS x [nb][2 rows][wt][64 ch]
   const u32 ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -64,6 +68,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
       mbar_init(oempty(i), 1);
     }
     abort_flag = 0;
+    dyn_count = 0;
     mbar_fence_init();
   }
   __syncthreads();
@@ -99,41 +104,61 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   if (warp >= NCW) {
     // the producer warpgroup keeps 24 registers per thread and frees the rest for the consumers
     if (Cfg::FWD_SETMAXNREG) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::FWD_REGS_PRODUCER));
+    // The first g.dyn_begin units of the flattened work are cut into equal static spans, one
+    // per CTA; the rest (none unless the launch asks for it) is a pool that the load warps
+    // claim from in pieces of g.dyn_chunk pairs, so that CTAs whose HBM traffic was served
+    // faster take more of the tail.  The load lane publishes every piece it claims in `dynq`
+    // for the store lanes, which walk the same sequence.
     const int total = g.n_chunks * g.n_ig * g.n_ct * g.n_pairs;
-    const int u0 = gw8_span_begin(total, blockIdx.x, gridDim.x);
-    const int u1 = gw8_span_begin(total, blockIdx.x + 1, gridDim.x);
+    const int n_static = g.dyn_chunk > 0 ? g.dyn_begin : total;
+    const int u0 = gw8_span_begin(n_static, blockIdx.x, gridDim.x);
+    const int u1 = gw8_span_begin(n_static, blockIdx.x + 1, gridDim.x);
     if (warp == NCW) {
       // ---------------------------------------------------------- load warp
       if (lane == 0) {
         prefetch_tensormap(&in_map);
         const u64 in_policy = make_l2_policy(g.hint_in);
-        Gw8Walk walk(u0, u1, g);
-        Gw8Segment seg;
         int slot = 0;
         u32 par = 0;
         bool ok = true;
-        while (ok && walk.next(seg)) {
-          const int nst = stages_of(seg);
-          const int len = seg.m1 - seg.m0;
-          const int c0 = seg.ck * 64;
-          const int w0 = seg.ct * g.wt - g.pad_w;
-          const int n0 = seg.ig * g.nb;
-          for (int i = 0; i < nst; ++i) {
-            if (!mbar_wait(empty(slot), par ^ 1u, abortp)) {
-              ok = false;
-              break;
+        auto load_span = [&](int ua, int ub) {
+          Gw8Walk walk(ua, ub, g);
+          Gw8Segment seg;
+          while (ok && walk.next(seg)) {
+            const int nst = stages_of(seg);
+            const int len = seg.m1 - seg.m0;
+            const int c0 = seg.ck * 64;
+            const int w0 = seg.ct * g.wt - g.pad_w;
+            const int n0 = seg.ig * g.nb;
+            for (int i = 0; i < nst; ++i) {
+              if (!mbar_wait(empty(slot), par ^ 1u, abortp)) {
+                ok = false;
+                break;
+              }
+              desc[slot].ck = seg.ck;
+              desc[slot].mask = out_mask(i, len);
+              desc[slot].ph0 = (PPS * i) % NPH;
+              desc[slot].flags = 0;
+              mbar_arrive_expect_tx(full(slot), g.slot_bytes);
+              tma_load_4d(ring + (u32)slot * g.slot_bytes, &in_map, full(slot), c0, w0,
+                          2 * (seg.m0 + PPS * i) - g.pad_h, n0, g.hint_in, in_policy);
+              if (++slot == ns) {
+                slot = 0;
+                par ^= 1u;
+              }
             }
-            desc[slot].ck = seg.ck;
-            desc[slot].mask = out_mask(i, len);
-            desc[slot].ph0 = (PPS * i) % NPH;
-            desc[slot].flags = 0;
-            mbar_arrive_expect_tx(full(slot), g.slot_bytes);
-            tma_load_4d(ring + (u32)slot * g.slot_bytes, &in_map, full(slot), c0, w0,
-                        2 * (seg.m0 + PPS * i) - g.pad_h, n0, g.hint_in, in_policy);
-            if (++slot == ns) {
-              slot = 0;
-              par ^= 1u;
-            }
+          }
+        };
+        load_span(u0, u1);
+        if (g.dyn_chunk > 0) {
+          int k = 0;
+          while (ok) {
+            const int u = g.dyn_begin + atomicAdd(status + 1 + g.dyn_slot, g.dyn_chunk);
+            dynq[k & (DYNQ - 1)] = u < total ? u : -1;  // -1: the pool is empty
+            __threadfence_block();
+            *dyn_n = ++k;
+            if (u >= total) break;
+            load_span(u, u + g.dyn_chunk < total ? u + g.dyn_chunk : total);
           }
         }
         if (ok && mbar_wait(empty(slot), par ^ 1u, abortp)) {
@@ -148,38 +173,64 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
       // it.  Bulk groups are tracked per thread, so the buffers drain independently.
       if (lane < nob) {
         prefetch_tensormap(&out_map);
-        Gw8Walk walk(u0, u1, g);
-        Gw8Segment seg;
         int turn = 0;  // which buffer the next stage goes to
         u32 opar = 0;  // parity of this lane's next use of its buffer
         bool ok = true;
-        while (ok && walk.next(seg)) {
-          const int nst = stages_of(seg);
-          const int len = seg.m1 - seg.m0;
-          const int c0 = seg.ck * 64;
-          const int w0 = seg.ct * g.wt;
-          const int n0 = seg.ig * g.nb;
-          for (int i = 0; i < nst; ++i) {
-            const int mask = out_mask(i, len);
-            if (mask == 0) continue;
-            if (turn == lane) {
-              if (!mbar_wait(ofull(lane), opar, abortp)) {
-                ok = false;
-                break;
-              }
+        auto store_span = [&](int ua, int ub) {
+          Gw8Walk walk(ua, ub, g);
+          Gw8Segment seg;
+          while (ok && walk.next(seg)) {
+            const int nst = stages_of(seg);
+            const int len = seg.m1 - seg.m0;
+            const int c0 = seg.ck * 64;
+            const int w0 = seg.ct * g.wt;
+            const int n0 = seg.ig * g.nb;
+            for (int i = 0; i < nst; ++i) {
+              const int mask = out_mask(i, len);
+              if (mask == 0) continue;
+              if (turn == lane) {
+                if (!mbar_wait(ofull(lane), opar, abortp)) {
+                  ok = false;
+                  break;
+                }
 #pragma unroll
-              for (int u = 0; u < PPS; ++u) {
-                if (mask & (1 << u))
-                  tma_store_4d(&out_map,
-                               obufs + (u32)lane * g.obuf_bytes + (u32)u * g.out_pair_bytes, c0, w0,
-                               2 * (seg.m0 + PPS * i + u - E), n0);
+                for (int u = 0; u < PPS; ++u) {
+                  if (mask & (1 << u))
+                    tma_store_4d(&out_map,
+                                 obufs + (u32)lane * g.obuf_bytes + (u32)u * g.out_pair_bytes, c0, w0,
+                                 2 * (seg.m0 + PPS * i + u - E), n0);
+                }
+                tma_store_commit();
+                tma_store_wait_read0();
+                mbar_arrive(oempty(lane));
+                opar ^= 1u;
               }
-              tma_store_commit();
-              tma_store_wait_read0();
-              mbar_arrive(oempty(lane));
-              opar ^= 1u;
+              if (++turn == nob) turn = 0;
             }
-            if (++turn == nob) turn = 0;
+          }
+        };
+        store_span(u0, u1);
+        if (g.dyn_chunk > 0) {
+          for (int k = 0; ok; ++k) {
+            // wait (bounded) until the load lane has published its k-th claim
+            u64 t0 = 0;
+            for (u32 it = 1; *dyn_n <= k; ++it) {
+              if ((it & 63u) == 0u) {
+                if (*abortp) ok = false;
+                const u64 now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > SPIO_WAIT_LIMIT_NS) {
+                  *abortp = 1;
+                  ok = false;
+                }
+                if (!ok) break;
+              }
+            }
+            if (!ok) break;
+            __threadfence_block();
+            const int u = dynq[k & (DYNQ - 1)];
+            if (u < 0) break;
+            store_span(u, u + g.dyn_chunk < total ? u + g.dyn_chunk : total);
           }
         }
         tma_store_wait_all();
@@ -394,6 +445,13 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   // them either: a later kernel that waits for this one relies on that to be ordered after
   // the whole chain.  By now they have long finished, so this returns at once.
   if (g.independent) grid_dependency_wait();
+  if (g.dyn_chunk > 0 && threadIdx.x == 0) {
+    // every load warp has seen the pool empty by now; the last CTA to leave clears the counters
+    if (atomicAdd(status + 1 + GW8_DYN_SLOTS + g.dyn_slot, 1) == (int)gridDim.x - 1) {
+      status[1 + g.dyn_slot] = 0;
+      status[1 + GW8_DYN_SLOTS + g.dyn_slot] = 0;
+    }
+  }
   if (abort_flag) {
     // Let copies that may still be in flight land before the CTA gives up its
     // shared memory, then report.

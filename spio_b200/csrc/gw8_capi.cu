@@ -10,6 +10,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -45,7 +46,7 @@ int fail_cuda(const char* what, cudaError_t e) {
 
 // Status word the kernels write when a bounded wait gives up; one per device because
 // the symbol is instantiated in every context that loads the library.
-__device__ int g_status_word;
+__device__ int g_status_word[1 + 2 * GW8_DYN_SLOTS];  // status, claim counters, exit counters
 
 constexpr int kMaxDevices = 64;
 
@@ -112,7 +113,7 @@ int device_info(const DeviceInfo** out) {
     if (major != 10)
       return fail("unsupported device: libspio_b200 is built for sm_100a only");
     GW8_CUDA(cudaGetSymbolAddress((void**)&d.status, g_status_word));
-    GW8_CUDA(cudaMemset(d.status, 0, sizeof(int)));
+    GW8_CUDA(cudaMemset(d.status, 0, sizeof(g_status_word)));
     if (g_encode == nullptr) {
       void* fn = nullptr;
       cudaDriverEntryPointQueryResult qres;
@@ -259,6 +260,16 @@ int make_plan_tc(int kind, const spio_gw8_shape* sh, const spio_gw8_tune& t, int
   pl.grid = (int)(total < ctas ? total : ctas);
   *plan = pl;
   return 0;
+}
+
+// SPIO_DYN=<pairs per claim> turns the dynamic tail of the forward kernel on (0 = off).
+int dyn_chunk_setting() {
+  static const int v = [] {
+    const char* e = getenv("SPIO_DYN");
+    const int n = e ? atoi(e) : 0;
+    return n > 0 && n <= 64 ? n : 0;
+  }();
+  return v;
 }
 
 int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
@@ -412,6 +423,15 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
   } else {
     pl.threads = v->fwd_threads;
     pl.grid = (int)(total < ctas ? total : ctas);
+    // Optional dynamic tail (SPIO_DYN = pairs per claim): the last 8 pairs per CTA on average
+    // are not assigned statically but claimed from a pool, when a CTA has enough work for it.
+    const int chunk = dyn_chunk_setting();
+    if (chunk > 0 && total >= 16LL * pl.grid * chunk / 4) {
+      long long pool = 2LL * chunk * pl.grid;
+      if (pool > total / 4) pool = total / 4;
+      g.dyn_chunk = chunk;
+      g.dyn_begin = (int)(total - pool);
+    }
   }
   *plan = pl;
   return 0;
@@ -487,6 +507,10 @@ int launch_fwd(int kind, void* out, const void* in, const void* w, const float* 
   if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
   pl.g.independent = (independent && pdl_enabled()) ? 1 : 0;
   pl.g.hint_in = hint_in;
+  if (pl.g.dyn_chunk > 0) {
+    static std::atomic<unsigned> next_slot{0};
+    pl.g.dyn_slot = (int)(next_slot.fetch_add(1) % GW8_DYN_SLOTS);
+  }
   if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
   if (pl.engine == 2) {
     const Gw8Geom& g = pl.g;

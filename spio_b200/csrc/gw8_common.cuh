@@ -27,6 +27,10 @@ struct alignas(64) TensorMap {
   unsigned long long opaque[16];
 };
 
+// The status word is followed by GW8_DYN_SLOTS claim counters and as many exit counters, all
+// zero between launches (the last CTA of a launch clears the pair it used).
+enum { GW8_DYN_SLOTS = 64 };
+
 enum Gw8Status {
   GW8_OK = 0,
   GW8_WAIT_TIMEOUT = 1,  // a bounded mbarrier wait gave up
@@ -56,6 +60,9 @@ struct Gw8Geom {
   int independent;     // 1: the caller guarantees that this launch neither reads nor overwrites
                        // anything the preceding kernels of its programmatic-launch chain write or
                        // read, so the kernel does not wait for them
+  int dyn_begin;       // forward kernel: first unit of the dynamically claimed pool
+  int dyn_chunk;       // pairs per claim; 0 = everything is split statically
+  int dyn_slot;        // which pair of counters behind the status word this launch uses
   int hint_in;         // L2 eviction hint (L2_HINT_*) for loads of the streamed operand
   int hint_tiled;      // wgrad: the same for loads of dy
   // byte sizes derived from the above (kept here so that the kernels read them from the

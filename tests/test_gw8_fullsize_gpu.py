@@ -110,3 +110,38 @@ def test_host_buffer_entry_points_match_device_entry_points():
     assert torch.equal(O.from_nhwc(hdx), capi.dgrad(dyd, wd, sh).cpu())
     assert torch.equal(O.from_nhwc(hdw), capi.wgrad(xd, dyd, sh).cpu())
     assert capi.status() == 0
+
+
+def test_dynamic_tail_gives_identical_results():
+    """SPIO_DYN=<pairs per claim> lets the forward kernel's load warps claim the tail of the
+    work from a global pool.  The setting is read once per process, so the comparison runs in
+    a child process: fprop and dgrad must be bit-identical with and without it, on a shape
+    large enough for the pool to be used and over repeated launches (the counters are reused)."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    code = textwrap.dedent("""
+        import sys, torch
+        from oracle import oracle as O
+        from tests import capi
+        sh = O.Shape(96, 72, 56, 56, 3, 3, 1, 1)
+        x, w, b, dy = O.make_inputs(sh, seed=31, bias=True)
+        xd, wd, bd, dyd = (capi.to_dev(t) for t in (x, w, b, dy))
+        outs = []
+        for _ in range(5):
+            outs.append((capi.fprop(xd, wd, bd, sh), capi.dgrad(dyd, wd, sh)))
+        assert all(torch.equal(outs[0][0], o[0]) and torch.equal(outs[0][1], o[1]) for o in outs)
+        assert capi.status() == 0
+        torch.save([t.cpu() for t in outs[0]], sys.argv[1])
+    """)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    results = []
+    for setting in ("0", "4"):
+        path = os.path.join(root, "tests", f"_dyn_{setting}.pt")
+        env = dict(os.environ, SPIO_DYN=setting, PYTHONPATH=root)
+        subprocess.run([sys.executable, "-c", code, path], check=True, env=env, cwd=root, timeout=300)
+        results.append(torch.load(path))
+        os.remove(path)
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
