@@ -262,11 +262,12 @@ int make_plan_tc(int kind, const spio_gw8_shape* sh, const spio_gw8_tune& t, int
   return 0;
 }
 
-// SPIO_DYN=<pairs per claim> turns the dynamic tail of the forward kernel on (0 = off).
+// Pairs per claim of the forward kernel's dynamic tail; SPIO_DYN=<n> changes it, SPIO_DYN=0
+// turns the dynamic tail off.
 int dyn_chunk_setting() {
   static const int v = [] {
     const char* e = getenv("SPIO_DYN");
-    const int n = e ? atoi(e) : 0;
+    const int n = e ? atoi(e) : 4;
     return n > 0 && n <= 64 ? n : 0;
   }();
   return v;
@@ -423,8 +424,8 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
   } else {
     pl.threads = v->fwd_threads;
     pl.grid = (int)(total < ctas ? total : ctas);
-    // Optional dynamic tail (SPIO_DYN = pairs per claim): the last 8 pairs per CTA on average
-    // are not assigned statically but claimed from a pool, when a CTA has enough work for it.
+    // Dynamic tail: the last 8 pairs per CTA on average are not assigned statically but claimed
+    // from a pool, when a CTA has enough work for it.
     const int chunk = dyn_chunk_setting();
     if (chunk > 0 && total >= 16LL * pl.grid * chunk / 4) {
       long long pool = 2LL * chunk * pl.grid;
@@ -508,8 +509,16 @@ int launch_fwd(int kind, void* out, const void* in, const void* w, const float* 
   pl.g.independent = (independent && pdl_enabled()) ? 1 : 0;
   pl.g.hint_in = hint_in;
   if (pl.g.dyn_chunk > 0) {
-    static std::atomic<unsigned> next_slot{0};
-    pl.g.dyn_slot = (int)(next_slot.fetch_add(1) % GW8_DYN_SLOTS);
+    // A launch recorded into a CUDA graph would keep its counter slot for every replay, and two
+    // graphs holding the same slot could run at the same time: recorded launches stay static.
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    GW8_CUDA(cudaStreamIsCapturing(stream, &capture));
+    if (capture != cudaStreamCaptureStatusNone) {
+      pl.g.dyn_chunk = 0;
+    } else {
+      static std::atomic<unsigned> next_slot{0};
+      pl.g.dyn_slot = (int)(next_slot.fetch_add(1) % GW8_DYN_SLOTS);
+    }
   }
   if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
   if (pl.engine == 2) {
