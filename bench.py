@@ -169,8 +169,6 @@ def run_ours(args) -> None:
     y = torch.empty_like(x)
     dx = torch.empty_like(x)
     dw = torch.empty(C, 8, R, S, device=dev, dtype=torch.float32).contiguous(memory_format=cl)
-    scratch_bytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(shp, None)
-    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=dev)
 
     main = torch.cuda.current_stream(dev)
     comm = torch.cuda.Stream(dev) if world > 1 else None
@@ -179,16 +177,26 @@ def run_ours(args) -> None:
     # Rank-local dgrad leaves one SM to the all-reduce kernel, which otherwise could not become
     # resident beside the persistent CTAs (one per SM) until they exit.
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    dgrad_tune = _clib.make_tune({"grid": sms - 1}) if world > 1 else None
+    tunes = json.loads(args.tune) if args.tune else {}
+    dgrad_cfg = dict(tunes.get("dgrad", {}))
+    if world > 1:
+        dgrad_cfg.setdefault("grid", sms - 1)
+    fprop_tune = _clib.make_tune(tunes["fprop"]) if tunes.get("fprop") else None
+    wgrad_tune = _clib.make_tune(tunes["wgrad"]) if tunes.get("wgrad") else None
+    dgrad_tune = _clib.make_tune(dgrad_cfg) if dgrad_cfg else None
+    fprop_tp = ctypes.byref(fprop_tune) if fprop_tune is not None else None
+    wgrad_tp = ctypes.byref(wgrad_tune) if wgrad_tune is not None else None
     dgrad_tp = ctypes.byref(dgrad_tune) if dgrad_tune is not None else None
+    scratch_bytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(shp, wgrad_tp)
+    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=dev)
     dw_ready = torch.cuda.Event()
     dw_ready.record(torch.cuda.current_stream(dev))  # creates the underlying CUDA event
 
     def fprop():
-        _clib.check(lib.spio_conv2d_gw8_fprop(y.data_ptr(), x.data_ptr(), w.data_ptr(), None, shp, None, sp))
+        _clib.check(lib.spio_conv2d_gw8_fprop(y.data_ptr(), x.data_ptr(), w.data_ptr(), None, shp, fprop_tp, sp))
 
     def wgrad():
-        _clib.check(lib.spio_conv2d_gw8_wgrad(dw.data_ptr(), x.data_ptr(), dy.data_ptr(), shp, None,
+        _clib.check(lib.spio_conv2d_gw8_wgrad(dw.data_ptr(), x.data_ptr(), dy.data_ptr(), shp, wgrad_tp,
                                               scratch.data_ptr(), scratch_bytes, sp))
 
     def dgrad():
@@ -197,7 +205,7 @@ def run_ours(args) -> None:
     def backward():
         # wgrad -> reduce -> (dw_ready) -> dgrad, chained with programmatic dependent launch
         _clib.check(lib.spio_conv2d_gw8_backward(
-            dx.data_ptr(), dw.data_ptr(), None, x.data_ptr(), dy.data_ptr(), w.data_ptr(), shp, dgrad_tp, None,
+            dx.data_ptr(), dw.data_ptr(), None, x.data_ptr(), dy.data_ptr(), w.data_ptr(), shp, dgrad_tp, wgrad_tp,
             scratch.data_ptr(), scratch_bytes, sp, dw_ready.cuda_event if comm is not None else None))
 
     def step(events=None):
@@ -322,7 +330,7 @@ def run_ours(args) -> None:
             "data": "synthetic",
             "config": {"workload": wl, "global_batch": GB, "per_rank_batch": n,
                        "l2": "every streamed operand > L2 (126 MB); no flush between steps",
-                       "parallelism": f"dp{world}"},
+                       "parallelism": f"dp{world}", "tune": tunes or "planner defaults"},
             "images_per_s": GB / (ms_per_step * 1e-3),
             "frac_of_8TBps_nominal": step_bytes_all / world / (ms_per_step * 1e-3) / 1e9 / 8000.0,
             "kernels_note": "per-kernel times come from a second pass of the same steps with CUDA events "
@@ -428,6 +436,8 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="images over all ranks (default: the 2048 of the data-parallel sweep)")
+    ap.add_argument("--tune", default="",
+                    help='JSON overrides of the launch plans, e.g. \'{"fprop": {"pps": 1}, "wgrad": {"ns": 4}}\'')
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -57,7 +57,13 @@ def compiled_variants(r: int, s: int) -> List[tuple]:
     return out
 
 
-def plan_is_valid(kind: int, params, tune: dict, device_attr) -> bool:
+# Forward configurations with an explicit ring depth stay within the 196 KiB shared-memory
+# configuration of the SM: in a chain of dependent launches the larger one costs 4-5 % per step
+# (the planner's own choice, ns = 0, follows the same rule).
+SMEM_SOFT_CAP = 195 * 1024
+
+
+def plan_is_valid(kind: int, params, tune: dict, device_attr, smem_cap: int = 0) -> bool:
     lib = _clib.load()
     info = _clib.PlanInfo()
     t = _clib.make_tune(tune)
@@ -65,7 +71,7 @@ def plan_is_valid(kind: int, params, tune: dict, device_attr) -> bool:
                                       device_attr.multiprocessor_count,
                                       device_attr.max_shared_memory_per_block_optin,
                                       ctypes.byref(info))
-    return rc == 0
+    return rc == 0 and (smem_cap <= 0 or info.smem_bytes <= smem_cap)
 
 
 def enumerate_tiles(params, out_w: int, wpg: int, tpw: int, forward: bool = False) -> Iterator[tuple]:
@@ -100,7 +106,7 @@ def _get_configs(params: Conv2dGw8Params, device_attr, igrad: bool = False) -> I
             for ns in (0, 3, 4, 6):
                 for nob in (2, 3):
                     cfg = Conv2dGw8Config(wpg=wpg, tpw=tpw, pps=pps, ncb=ncb, nb=nb, ns=ns, nob=nob)
-                    if plan_is_valid(kind, params, cfg.as_tune(), device_attr):
+                    if plan_is_valid(kind, params, cfg.as_tune(), device_attr, SMEM_SOFT_CAP if ns else 0):
                         yield cfg
     if params.r <= 3 and params.s <= 3:
         # the tcgen05 kernel: column tiles of up to 64 - (s - 1) pixels, ring depth, staging buffers
