@@ -262,14 +262,18 @@ int make_plan_tc(int kind, const spio_gw8_shape* sh, const spio_gw8_tune& t, int
   return 0;
 }
 
-// Soft cap on the forward kernel's shared memory.  A chain of kernels launched with programmatic
-// dependent launch (fprop -> wgrad -> reduce -> dgrad -> fprop ...) ran 4-5 % faster per step on
-// 56 x 56 and 112 x 112 images when the forward kernel stayed within the 196 KiB shared-memory
-// configuration of the SM instead of the 228 KiB one (measured with the same ring depth and padded
-// shared memory: the size decides, not the depth); each kernel timed alone runs the same either way.
-// The planner's own choice of ring depth therefore stops at this size while at least 3 slots remain;
-// an explicit ns in the tune is taken as given.
-constexpr int kSmemSoftCap = 195 * 1024;
+// Soft cap on shared memory: stay inside the SM's 196 KiB shared-memory configuration (dynamic +
+// static + 1 KiB reserved per CTA) instead of the 228 KiB one, which leaves only 28 KiB of L1.
+// The kernels with the largest tiles keep a small stack frame (16-64 bytes per thread of spilled
+// loop invariants); for the 544 threads of the weight-gradient kernel that is more than the 28 KiB
+// L1 holds, and every reload then goes to L2.  Measured: wgrad on 256 x 256 x 28 x 28 takes 67.5 us
+// with a 3-slot ring of 217 KiB and 49.9 us with 2 slots of 145 KiB.  The configuration is
+// sticky across dependent launches: after a forward kernel with 217 KiB the following wgrad ran
+// in the 228 KiB configuration although it needs 181 KiB (fprop + backward at N = 256 on
+// 64 x 56 x 56: 141.0 us per step, 134.0 us with the forward ring capped); kernels separated by
+// an idle SM get the configuration they need.  The planner's own choice of ring depth therefore
+// stops at this size while 3 (forward) or 2 (wgrad) slots remain; an explicit ns is taken as given.
+constexpr int kSmemSoftCap = 194 * 1024;
 
 // Pairs per claim of the forward kernel's dynamic tail; SPIO_DYN=<n> changes it, SPIO_DYN=0
 // turns the dynamic tail off.
@@ -378,8 +382,10 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
     }
     if (ns > 16) ns = 16;
     if (!t.ns && ns > 8) ns = 8;  // a deeper ring buys nothing and shrinks the L1 cache
-    if (!t.ns && kind != SPIO_GW8_WGRAD) {
-      while (ns > 3 && kAlignSlack + ns * slot + nob * oslot > kSmemSoftCap) --ns;
+    if (!t.ns) {
+      const int stage = kind == SPIO_GW8_WGRAD ? slot + oslot : slot;
+      const int ns_floor = kind == SPIO_GW8_WGRAD ? 2 : 3;
+      while (ns > ns_floor && kAlignSlack + ns * stage + nob * oslot > kSmemSoftCap) --ns;
     }
     if (t.ns) {
       if (t.ns > ns) return fail("requested ring does not fit in shared memory");

@@ -57,10 +57,11 @@ def compiled_variants(r: int, s: int) -> List[tuple]:
     return out
 
 
-# Forward configurations with an explicit ring depth stay within the 196 KiB shared-memory
-# configuration of the SM: in a chain of dependent launches the larger one costs 4-5 % per step
-# (the planner's own choice, ns = 0, follows the same rule).
-SMEM_SOFT_CAP = 195 * 1024
+# Configurations with an explicit ring depth stay within the 196 KiB shared-memory configuration
+# of the SM: the 228 KiB one leaves 28 KiB of L1, too little for the kernels' spilled loop
+# invariants, and it is sticky across dependent launches (the planner's own choice, ns = 0,
+# follows the same rule).
+SMEM_SOFT_CAP = 194 * 1024
 
 
 def plan_is_valid(kind: int, params, tune: dict, device_attr, smem_cap: int = 0) -> bool:

@@ -11,7 +11,7 @@ from dataclasses import asdict, dataclass
 from typing import Iterator
 
 from .. import _clib
-from .conv2d_gw8_kernel import compiled_variants, enumerate_tiles, plan_is_valid
+from .conv2d_gw8_kernel import SMEM_SOFT_CAP, compiled_variants, enumerate_tiles, plan_is_valid
 from .conv2d_gw8_params import Conv2dGw8Params
 from .conv2d_stats import Conv2dStats
 from .kernel_factory import KernelFactory
@@ -35,7 +35,7 @@ def _get_configs(params: Conv2dGw8Params, device_attr) -> Iterator[Conv2dGw8Wgra
         for ncb, nb in enumerate_tiles(params, params.q, wpg, tpw):
             for ns in (0, 2, 3, 4):
                 cfg = Conv2dGw8WgradConfig(wpg=wpg, tpw=tpw, pps=pps, ncb=ncb, nb=nb, ns=ns)
-                if plan_is_valid(_clib.WGRAD, params, cfg.as_tune(), device_attr):
+                if plan_is_valid(_clib.WGRAD, params, cfg.as_tune(), device_attr, SMEM_SOFT_CAP if ns else 0):
                     yield cfg
 
 
