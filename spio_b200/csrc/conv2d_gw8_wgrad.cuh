@@ -161,15 +161,23 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     // dy: matrix 0 = the 8 pixels of the top row, matrix 1 = bottom row
     const u32 dy_off = ((u32)((lane >> 3) & 1) * (u32)g.wt + l7) * 128u + (((u32)grp ^ l7) << 4);
 
+    // Tile t of this warp is tile wsub + WPG * t of the slot.  With one image per slot (NB1,
+    // every image wide enough to fill the warps) its offset inside the x rows and the dy rows
+    // is the same compile-time multiple of 8 pixels past the warp's first tile, so it costs no
+    // registers; with several images per slot the offsets are kept per tile.
+    auto compute = [&](auto nb1c) {
+    constexpr bool NB1 = decltype(nb1c)::value != 0;
     u32 x_off[TPW], d_off[TPW];
-    bool tile_on[TPW];
+    const u32 t_off0 = (u32)wsub * 1024u;
+    auto tile_on = [&](int t) { return wsub + WPG * t < g.ntiles; };
 #pragma unroll
     for (int t = 0; t < TPW; ++t) {
       const int tidx = wsub + WPG * t;
-      tile_on[t] = tidx < g.ntiles;
-      const int img = tidx / g.ncb, cb = tidx % g.ncb;
-      x_off[t] = (u32)(img * 2 * PPS * g.bw + cb * 8) * 128u;
-      d_off[t] = (u32)(img * 2 * PPS * g.wt + cb * 8) * 128u;
+      if (!NB1) {
+        const int img = tidx / g.ncb, cb = tidx % g.ncb;
+        x_off[t] = (u32)(img * 2 * PPS * g.bw + cb * 8) * 128u;
+        d_off[t] = (u32)(img * 2 * PPS * g.wt + cb * 8) * 128u;
+      }
     }
 
     u32 X[TPW][WIN][S];
@@ -178,12 +186,6 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     u32 par = 0;
     bool ok = true;
     bool full_seen = mbar_test_wait(full(0), 0u);
-    const bool cta_sum = WPG > 1 && !g.warp_parts;
-    const int n_parts = cta_sum ? g.n_split : g.n_split * WPG;
-    // Staging for the in-CTA sum of the WPG warps of a group.  It reuses the ring: a CTA
-    // that sums in shared memory works on one chunk only, so when it flushes every slot has
-    // been consumed and the load warp has nothing left to issue.
-    float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
 
     for (int ck = cl; ok && ck < g.n_chunks; ck += chunk_step) {
       const bool grp_on = (ck * 64 + grp * 8) < g.c;
@@ -201,7 +203,7 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
         auto stage = [&](auto ph0c, int i) -> bool {
           constexpr int PH0 = decltype(ph0c)::value;
           if (!full_seen && !mbar_wait(full(slot), par, abortp)) return false;
-          const u32 xbase = base + (u32)slot * stage_bytes;
+          const u32 xbase = base + (u32)slot * stage_bytes + (NB1 ? t_off0 : 0u);
           const u32 dbase = xbase + xslot_bytes;
           if (grp_on) {
 #pragma unroll
@@ -211,8 +213,9 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
               const bool pair_on = q >= 0 && q < len;
 #pragma unroll
               for (int t = 0; t < TPW; ++t) {
-                if (tile_on[t]) {
-                  const u32 a = opaque_add(xbase, x_off[t]) + (u32)u * x_pair_bytes;
+                if (tile_on(t)) {
+                  const u32 a = (NB1 ? xbase + (u32)(t * WPG) * 1024u : opaque_add(xbase, x_off[t])) +
+                                (u32)u * x_pair_bytes;
 #pragma unroll
                   for (int v = 0; v < NLD4; ++v) {
                     const int f0 = 4 * v;
@@ -229,7 +232,8 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
                   }
                   if (pair_on) {
                     u32 d0, d1;
-                    ldmatrix_x2<true>(d0, d1, opaque_add(dbase, d_off[t]) + (u32)u * d_pair_bytes + dy_off);
+                    ldmatrix_x2<true>(d0, d1, (NB1 ? dbase + (u32)(t * WPG) * 1024u : opaque_add(dbase, d_off[t])) +
+                                                  (u32)u * d_pair_bytes + dy_off);
 #pragma unroll
                     for (int k = 0; k < NACC; ++k) {
                       const int fa = 2 * k, fb = 2 * k + 1;
@@ -274,6 +278,12 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
 
       // Sum the WPG warps of each group inside the CTA, then flush one partial per CTA:
       // acc[i] = {(tap 2i, c=g, k=2t), (.., k=2t+1), (tap 2i+1, c=g, k=2t), (.., k=2t+1)}.
+      // The staging for that sum reuses the ring: a CTA that sums in shared memory works on one
+      // chunk only, so when it flushes every slot has been consumed and the load warp has
+      // nothing left to issue.
+      const bool cta_sum = WPG > 1 && !g.warp_parts;
+      const int n_parts = cta_sum ? g.n_split : g.n_split * WPG;
+      float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
       if (cta_sum) {
         // every compute warp must have finished reading the ring before it is overwritten
         asm volatile("bar.sync 1, %0;" ::"r"(NCW * 32) : "memory");
@@ -317,6 +327,11 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
         }
       }
     }
+    };  // compute
+    if (g.nb == 1)
+      compute(IntC<1>{});
+    else
+      compute(IntC<0>{});
   }
 
   __syncthreads();
