@@ -186,6 +186,13 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     u32 par = 0;
     bool ok = true;
     bool full_seen = mbar_test_wait(full(0), 0u);
+    // Running addresses of this lane's ldmatrix rows in the current slot (x: A, dy: Dp); they
+    // advance by one stage per hand-off and wrap with the ring, which keeps the slot base, the
+    // lane offsets and the x / dy split out of the registers that live across the loop.
+    u32 A[NLD];
+#pragma unroll
+    for (int q = 0; q < NLD; ++q) A[q] = base + (NB1 ? t_off0 : 0u) + ld_off[q];
+    u32 Dp = base + (NB1 ? t_off0 : 0u) + xslot_bytes + dy_off;
 
     for (int ck = cl; ok && ck < g.n_chunks; ck += chunk_step) {
       const bool grp_on = (ck * 64 + grp * 8) < g.c;
@@ -203,8 +210,6 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
         auto stage = [&](auto ph0c, int i) -> bool {
           constexpr int PH0 = decltype(ph0c)::value;
           if (!full_seen && !mbar_wait(full(slot), par, abortp)) return false;
-          const u32 xbase = base + (u32)slot * stage_bytes + (NB1 ? t_off0 : 0u);
-          const u32 dbase = xbase + xslot_bytes;
           if (grp_on) {
 #pragma unroll
             for (int u = 0; u < PPS; ++u) {
@@ -214,26 +219,27 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
 #pragma unroll
               for (int t = 0; t < TPW; ++t) {
                 if (tile_on(t)) {
-                  const u32 a = (NB1 ? xbase + (u32)(t * WPG) * 1024u : opaque_add(xbase, x_off[t])) +
-                                (u32)u * x_pair_bytes;
+                  // row pair u of tile t: (2 * bw) pixels of 128 bytes per pair
+                  const u32 xu = (u32)u * ((u32)g.bw << 8);
+                  const u32 ao = NB1 ? (u32)(t * WPG) * 1024u + xu : opaque_add(x_off[t], xu);
 #pragma unroll
                   for (int v = 0; v < NLD4; ++v) {
                     const int f0 = 4 * v;
                     ldmatrix_x4<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
                                       X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
                                       X[t][2 * PH + (f0 + 2) / S][(f0 + 2) % S],
-                                      X[t][2 * PH + (f0 + 3) / S][(f0 + 3) % S], a + ld_off[v]);
+                                      X[t][2 * PH + (f0 + 3) / S][(f0 + 3) % S], A[v] + ao);
                   }
                   if (LD2) {
                     const int f0 = 4 * NLD4;
                     ldmatrix_x2<true>(X[t][2 * PH + (f0 + 0) / S][(f0 + 0) % S],
                                       X[t][2 * PH + (f0 + 1) / S][(f0 + 1) % S],
-                                      a + ld_off[NLD - 1]);
+                                      A[NLD - 1] + ao);
                   }
                   if (pair_on) {
                     u32 d0, d1;
-                    ldmatrix_x2<true>(d0, d1, (NB1 ? dbase + (u32)(t * WPG) * 1024u : opaque_add(dbase, d_off[t])) +
-                                                  (u32)u * d_pair_bytes + dy_off);
+                    const u32 du = (u32)u * ((u32)g.wt << 8);
+                    ldmatrix_x2<true>(d0, d1, Dp + (NB1 ? (u32)(t * WPG) * 1024u + du : opaque_add(d_off[t], du)));
 #pragma unroll
                     for (int k = 0; k < NACC; ++k) {
                       const int fa = 2 * k, fb = 2 * k + 1;
@@ -257,9 +263,16 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(empty(slot));
+#pragma unroll
+          for (int q = 0; q < NLD; ++q) A[q] += stage_bytes;
+          Dp += stage_bytes;
           if (++slot == ns) {
             slot = 0;
             par ^= 1u;
+            const u32 ring = (u32)ns * stage_bytes;
+#pragma unroll
+            for (int q = 0; q < NLD; ++q) A[q] -= ring;
+            Dp -= ring;
           }
           full_seen = mbar_test_wait(full(slot), par);
           return true;
