@@ -43,7 +43,7 @@ L2_BYTES = 126 * 1024 * 1024
 # the 126 MB L2 when the kernel ends.  Reads and writes grow with the batch, the L2 residue
 # does not, so a launch at another batch is estimated as below.
 FWD_DRAM_READ_RATIO = 1.015
-FWD_L2_RESIDUE_BYTES = 51.7e6
+FWD_L2_RESIDUE_BYTES = 47.7e6
 
 
 def fwd_dram_traffic(algorithmic: int) -> float:
