@@ -271,11 +271,13 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
 
     // Block tile t of this warp: image img of the slot, first pixel px0 of the block.
     u32 tile_code[TPW];  // (img << 16) | (px0 * 128)
-    bool tile_on[TPW];
+    // Tiles wsub + WPG * t below `tiles_live` are computed: the slot's tile count, or none while
+    // the warp's channel group lies beyond the last channel.
+    int tiles_live = 0;
+    auto tile_on = [&](int t) { return wsub + WPG * t < tiles_live; };
 #pragma unroll
     for (int t = 0; t < TPW; ++t) {
       const int tidx = wsub + WPG * t;
-      tile_on[t] = tidx < g.ntiles;
       const int blk = tidx % g.nblk;
       int px0 = 16 * blk;
       if (px0 > g.wt - 16) px0 = g.wt - 16;  // the last block is shifted left, never past the tile
@@ -306,10 +308,10 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
 #pragma unroll
       for (int u = 0; u < PPS; ++u) {
         const int PH = (PH0 + u) % NPH;
-        if (grp_on) {
+        {
 #pragma unroll
           for (int t = 0; t < TPW; ++t) {
-            if (tile_on[t]) {
+            if (tile_on(t)) {
               const u32 a = opaque_add(sbase, in_off(t)) + (u32)u * g.in_pair_bytes;
 #pragma unroll
               for (int row = 0; row < 2; ++row) {
@@ -340,10 +342,10 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
             if (!mbar_wait(oempty(ob), opar ^ 1u, abortp)) return false;
             obuf_seen = true;
           }
-          if (grp_on) {
+          {
 #pragma unroll
             for (int t = 0; t < TPW; ++t) {
-              if (tile_on[t]) {
+              if (tile_on(t)) {
                 const u32 o = opaque_add(obase, out_off(t)) + (u32)u * g.out_pair_bytes + st_off;
 #pragma unroll
                 for (int y = 0; y < 2; ++y) {  // the two output rows of the pair
@@ -404,6 +406,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
         const int t4 = lane & 3;   // fragment pair index "t"
         const int ch0 = d.x * 64 + grp * 8;  // first channel of this warp's group
         grp_on = ch0 < g.c;
+        tiles_live = grp_on ? g.ntiles : 0;
         bias0 = bias1 = 0.f;
 #pragma unroll
         for (int f = 0; f < NT; ++f) wreg[f] = 0u;
