@@ -300,8 +300,10 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
     bool full_seen = mbar_test_wait(full(0), 0u);  // poll issued ahead of its use
 
     // One stage.  PH0 fixes which physical window rows the PPS sub-steps overwrite.
-    auto stage = [&](auto ph0c, const int mask) -> bool {
+    // ALL: every tile of the warp is live (the usual case), no per-tile tests.
+    auto stage = [&](auto ph0c, auto allc, const int mask) -> bool {
       constexpr int PH0 = decltype(ph0c)::value;
+      constexpr bool ALL = decltype(allc)::value != 0;
       const u32 sbase = ring + (u32)slot * g.slot_bytes;
       bool obuf_seen = mask ? mbar_test_wait(oempty(ob), opar ^ 1u) : true;
       const u32 obase = obufs + (u32)ob * g.obuf_bytes;
@@ -311,7 +313,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
         {
 #pragma unroll
           for (int t = 0; t < TPW; ++t) {
-            if (tile_on(t)) {
+            if (ALL || tile_on(t)) {
               const u32 a = opaque_add(sbase, in_off(t)) + (u32)u * g.in_pair_bytes;
 #pragma unroll
               for (int row = 0; row < 2; ++row) {
@@ -345,7 +347,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
           {
 #pragma unroll
             for (int t = 0; t < TPW; ++t) {
-              if (tile_on(t)) {
+              if (ALL || tile_on(t)) {
                 const u32 o = opaque_add(obase, out_off(t)) + (u32)u * g.out_pair_bytes + st_off;
 #pragma unroll
                 for (int y = 0; y < 2; ++y) {  // the two output rows of the pair
@@ -433,12 +435,21 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
         }
       }
       bool ok;
-      if (d.z == 0)
-        ok = stage(IntC<0>{}, d.y);
-      else if (d.z == 1)
-        ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, d.y);
-      else
-        ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, d.y);
+      if (tiles_live >= WPG * TPW) {
+        if (d.z == 0)
+          ok = stage(IntC<0>{}, IntC<1>{}, d.y);
+        else if (d.z == 1)
+          ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, IntC<1>{}, d.y);
+        else
+          ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, IntC<1>{}, d.y);
+      } else {
+        if (d.z == 0)
+          ok = stage(IntC<0>{}, IntC<0>{}, d.y);
+        else if (d.z == 1)
+          ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, IntC<0>{}, d.y);
+        else
+          ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, IntC<0>{}, d.y);
+      }
       if (!ok) break;
     }
   }

@@ -169,7 +169,8 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     constexpr bool NB1 = decltype(nb1c)::value != 0;
     u32 x_off[TPW], d_off[TPW];
     const u32 t_off0 = (u32)wsub * 1024u;
-    auto tile_on = [&](int t) { return wsub + WPG * t < g.ntiles; };
+    int tiles_live = 0;  // tiles of the slot this warp computes; none beyond the last channel
+    auto tile_on = [&](int t) { return wsub + WPG * t < tiles_live; };
 #pragma unroll
     for (int t = 0; t < TPW; ++t) {
       const int tidx = wsub + WPG * t;
@@ -195,7 +196,7 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
     u32 Dp = base + (NB1 ? t_off0 : 0u) + xslot_bytes + dy_off;
 
     for (int ck = cl; ok && ck < g.n_chunks; ck += chunk_step) {
-      const bool grp_on = (ck * 64 + grp * 8) < g.c;
+      tiles_live = (ck * 64 + grp * 8) < g.c ? g.ntiles : 0;
 #pragma unroll
       for (int i = 0; i < NACC; ++i)
 #pragma unroll
@@ -210,7 +211,7 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
         auto stage = [&](auto ph0c, int i) -> bool {
           constexpr int PH0 = decltype(ph0c)::value;
           if (!full_seen && !mbar_wait(full(slot), par, abortp)) return false;
-          if (grp_on) {
+          {
 #pragma unroll
             for (int u = 0; u < PPS; ++u) {
               const int PH = (PH0 + u) % NPH;
