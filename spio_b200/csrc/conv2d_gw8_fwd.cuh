@@ -301,11 +301,13 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
 
     // One stage.  PH0 fixes which physical window rows the PPS sub-steps overwrite.
     // ALL: every tile of the warp is live (the usual case), no per-tile tests.
-    auto stage = [&](auto ph0c, auto allc, const int mask) -> bool {
+    // FULL: every sub-step completes an output pair (the interior of an image), no mask tests.
+    auto stage = [&](auto ph0c, auto allc, auto fullc, const int mask) -> bool {
       constexpr int PH0 = decltype(ph0c)::value;
       constexpr bool ALL = decltype(allc)::value != 0;
+      constexpr bool FULL = decltype(fullc)::value != 0;
       const u32 sbase = ring + (u32)slot * g.slot_bytes;
-      bool obuf_seen = mask ? mbar_test_wait(oempty(ob), opar ^ 1u) : true;
+      bool obuf_seen = (FULL || mask) ? mbar_test_wait(oempty(ob), opar ^ 1u) : true;
       const u32 obase = obufs + (u32)ob * g.obuf_bytes;
 #pragma unroll
       for (int u = 0; u < PPS; ++u) {
@@ -339,7 +341,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
           }
           full_seen = mbar_test_wait(full(slot), par);
         }
-        if (mask & (1 << u)) {  // this sub-step completes an output pair
+        if (FULL || (mask & (1 << u))) {  // this sub-step completes an output pair
           if (!obuf_seen) {
             if (!mbar_wait(oempty(ob), opar ^ 1u, abortp)) return false;
             obuf_seen = true;
@@ -386,7 +388,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
           }
         }
       }
-      if (mask) {
+      if (FULL || mask) {
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(ofull(ob));
@@ -434,21 +436,19 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
           }
         }
       }
+      auto run = [&](auto allc, auto fullc) -> bool {
+        if (d.z == 0) return stage(IntC<0>{}, allc, fullc, d.y);
+        if (d.z == 1) return stage(IntC<(NPH > 1 ? 1 : 0)>{}, allc, fullc, d.y);
+        return stage(IntC<(NPH > 2 ? 2 : 0)>{}, allc, fullc, d.y);
+      };
       bool ok;
       if (tiles_live >= WPG * TPW) {
-        if (d.z == 0)
-          ok = stage(IntC<0>{}, IntC<1>{}, d.y);
-        else if (d.z == 1)
-          ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, IntC<1>{}, d.y);
+        if (d.y == (1 << PPS) - 1)
+          ok = run(IntC<1>{}, IntC<1>{});
         else
-          ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, IntC<1>{}, d.y);
+          ok = run(IntC<1>{}, IntC<0>{});
       } else {
-        if (d.z == 0)
-          ok = stage(IntC<0>{}, IntC<0>{}, d.y);
-        else if (d.z == 1)
-          ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, IntC<0>{}, d.y);
-        else
-          ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, IntC<0>{}, d.y);
+        ok = run(IntC<0>{}, IntC<0>{});
       }
       if (!ok) break;
     }

@@ -208,18 +208,22 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
         const int nst = stages_of(seg);
         const int len = seg.m1 - seg.m0;
 
-        auto stage = [&](auto ph0c, int i) -> bool {
+        // ALL: every tile of the warp is live; FULL: every sub-step has its dy pair (the interior
+        // of an image): the usual case runs without per-tile and per-pair tests.
+        auto stage = [&](auto ph0c, auto allc, auto fullc, int i) -> bool {
           constexpr int PH0 = decltype(ph0c)::value;
+          constexpr bool ALL = decltype(allc)::value != 0;
+          constexpr bool FULL = decltype(fullc)::value != 0;
           if (!full_seen && !mbar_wait(full(slot), par, abortp)) return false;
           {
 #pragma unroll
             for (int u = 0; u < PPS; ++u) {
               const int PH = (PH0 + u) % NPH;
               const int q = PPS * i + u - E;
-              const bool pair_on = q >= 0 && q < len;
+              const bool pair_on = FULL || (q >= 0 && q < len);
 #pragma unroll
               for (int t = 0; t < TPW; ++t) {
-                if (tile_on(t)) {
+                if (ALL || tile_on(t)) {
                   // row pair u of tile t: (2 * bw) pixels of 128 bytes per pair
                   const u32 xu = (u32)u * ((u32)g.bw << 8);
                   const u32 ao = NB1 ? (u32)(t * WPG) * 1024u + xu : opaque_add(x_off[t], xu);
@@ -279,14 +283,22 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
           return true;
         };
 
+        const bool all_live = wsub + WPG * (TPW - 1) < tiles_live;
         for (int i = 0; ok && i < nst; ++i) {
           const int ph0 = (PPS * i) % NPH;
-          if (ph0 == 0)
-            ok = stage(IntC<0>{}, i);
-          else if (ph0 == 1)
-            ok = stage(IntC<(NPH > 1 ? 1 : 0)>{}, i);
-          else
-            ok = stage(IntC<(NPH > 2 ? 2 : 0)>{}, i);
+          auto run = [&](auto allc, auto fullc) -> bool {
+            if (ph0 == 0) return stage(IntC<0>{}, allc, fullc, i);
+            if (ph0 == 1) return stage(IntC<(NPH > 1 ? 1 : 0)>{}, allc, fullc, i);
+            return stage(IntC<(NPH > 2 ? 2 : 0)>{}, allc, fullc, i);
+          };
+          if (all_live) {
+            if (PPS * i >= E && PPS * i + PPS - 1 - E < len)
+              ok = run(IntC<1>{}, IntC<1>{});
+            else
+              ok = run(IntC<1>{}, IntC<0>{});
+          } else {
+            ok = run(IntC<0>{}, IntC<0>{});
+          }
         }
       }
 
