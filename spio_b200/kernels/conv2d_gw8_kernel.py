@@ -18,7 +18,7 @@ takes ncb, ns and nob only.
 from __future__ import annotations
 
 import ctypes
-from dataclasses import asdict, dataclass
+from dataclasses import asdict, dataclass, replace
 from typing import Iterator, List
 
 from .. import _clib
@@ -120,6 +120,19 @@ def _get_configs(params: Conv2dGw8Params, device_attr, igrad: bool = False) -> I
                         yield cfg
 
 
+def _cap_ring(params: Conv2dGw8Params, config: Conv2dGw8Config, device_attr, igrad: bool = False):
+    """Tuning-table entries measured one kernel at a time may ask for a ring above the soft
+    cap; in a chain of dependent launches that costs more than the deeper ring gains, so the
+    depth goes back to the planner (which stops at the cap)."""
+    if config.engine == 2 or not config.ns:
+        return config
+    kind = _clib.DGRAD if igrad else _clib.FPROP
+    if plan_is_valid(kind, params, config.as_tune(), device_attr, SMEM_SOFT_CAP):
+        return config
+    capped = replace(config, ns=0)
+    return capped if plan_is_valid(kind, params, capped.as_tune(), device_attr) else config
+
+
 def _get_kernel_name(igrad: bool = False) -> str:
     return "spio_conv2d_gw8_dgrad" if igrad else "spio_conv2d_gw8_fprop"
 
@@ -131,4 +144,5 @@ conv2d_gw8_kernel_factory = KernelFactory(
     kernel_name=_get_kernel_name,
     configs=_get_configs,
     perf_model_skip_params=["group_width", "stride"],
+    fixup=_cap_ring,
 )

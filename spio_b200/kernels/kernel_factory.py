@@ -35,13 +35,15 @@ class KernelFactory:
                  kernel_name: Union[str, Callable[..., str]] = None,
                  configs: Union[List[Any], Callable[..., Any]] = None,
                  perf_model_skip_params: Optional[List[str]] = None,
-                 args_checker=check_channels_last):
+                 args_checker=check_channels_last,
+                 fixup: Optional[Callable[..., Any]] = None):
         self.params_cls = params_cls
         self.config_cls = config_cls
         self.stats_cls = stats_cls
         self._kernel_name = kernel_name
         self._configs = configs
         self._args_checker = args_checker
+        self._fixup = fixup
         self._kernel_caches: Dict[str, Any] = {}
         self.per_model_skip_params = list(perf_model_skip_params or [])
 
@@ -50,6 +52,13 @@ class KernelFactory:
         if callable(self._configs):
             return self._configs(params, device_attr, **kwargs)
         return self._configs
+
+    def fixup_config(self, params, config, device_attr, **kwargs):
+        """A configuration read from a tuning table, adjusted to rules learned after the table
+        was measured (identity unless the factory was given a ``fixup``)."""
+        if self._fixup is None:
+            return config
+        return self._fixup(params, config, device_attr, **kwargs)
 
     def get_kernel_name(self, **kwargs) -> str:
         return self._kernel_name(**kwargs) if callable(self._kernel_name) else self._kernel_name

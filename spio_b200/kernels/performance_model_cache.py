@@ -104,7 +104,7 @@ class PerformanceModelCache:
         kernel_name = kernel_factory.get_kernel_name(**kernel_kwargs)
         entry = self._table(kernel_name, arch).get(params.encode())
         if entry is not None:
-            return kernel_factory.config_cls(**entry)
+            return kernel_factory.fixup_config(params, kernel_factory.config_cls(**entry), attr, **kernel_kwargs)
         model = self._model(kernel_name, arch)
         base = params_features(params, kernel_factory.per_model_skip_params)
         # the model is trusted only for filter sizes and image extents it was trained on

@@ -207,3 +207,23 @@ def test_every_plannable_shape_has_a_configuration():
         assert len(list(conv2d_gw8_kernel_factory.configs(p, B200_ATTRIBUTES))) > 0
         assert len(list(conv2d_gw8_kernel_factory.configs(p, B200_ATTRIBUTES, igrad=True))) > 0
         assert len(list(conv2d_gw8_wgrad_kernel_factory.configs(p, B200_ATTRIBUTES))) > 0
+
+
+def test_table_entries_are_capped_to_the_196_kib_configuration():
+    """A tuned entry that asks for a ring above the soft shared-memory cap hands the depth back
+    to the planner; entries within the cap, and tcgen05 entries, are left alone."""
+    from spio_b200.kernels import conv2d_gw8_kernel_factory as factory
+    from spio_b200.kernels.conv2d_gw8_kernel import SMEM_SOFT_CAP, plan_is_valid
+    from spio_b200 import _clib
+
+    params = Conv2dGw8Params(n=256, c=64, h=56, w=56, r=3, s=3, padding=1)
+    deep = Conv2dGw8Config(wpg=2, tpw=4, pps=2, ns=5, nob=2)
+    assert plan_is_valid(_clib.FPROP, params, deep.as_tune(), B200_ATTRIBUTES)
+    assert not plan_is_valid(_clib.FPROP, params, deep.as_tune(), B200_ATTRIBUTES, SMEM_SOFT_CAP)
+    fixed = factory.fixup_config(params, deep, B200_ATTRIBUTES)
+    assert fixed.ns == 0 and (fixed.wpg, fixed.tpw, fixed.pps, fixed.nob) == (2, 4, 2, 2)
+    assert plan_is_valid(_clib.FPROP, params, fixed.as_tune(), B200_ATTRIBUTES, SMEM_SOFT_CAP)
+    ok = Conv2dGw8Config(wpg=2, tpw=4, pps=2, ns=4, nob=2)
+    assert factory.fixup_config(params, ok, B200_ATTRIBUTES, igrad=True) == ok
+    tc = Conv2dGw8Config(engine=2, ns=6, nob=2)
+    assert factory.fixup_config(params, tc, B200_ATTRIBUTES) == tc
