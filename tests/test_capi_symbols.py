@@ -117,3 +117,22 @@ def test_planner_engine_2():
     assert plan(_clib.FPROP, Shape(8, 64, 20, 20, 5, 5, 2, 2), {"engine": 2})[0] != 0
     assert plan(_clib.FPROP, sh, {"engine": 2, "ncb": 8})[0] != 0
     assert plan(_clib.FPROP, sh, {"engine": 3})[0] != 0
+
+
+def test_planner_keeps_rings_inside_the_196_kib_configuration():
+    """The planner's own ring depth stops at the shared-memory soft cap while 3 (forward) or
+    2 (weight gradient) slots remain; an explicit depth is taken as given."""
+    from oracle.oracle import Shape
+
+    cap = 194 * 1024
+    rc, p = plan(_clib.FPROP, Shape(256, 64, 56, 56, 3, 3, 1, 1))
+    assert rc == 0 and p["ns"] == 4 and p["smem_bytes"] <= cap
+    rc, p = plan(_clib.DGRAD, Shape(256, 64, 56, 56, 3, 3, 1, 1), {"ns": 5})
+    assert rc == 0 and p["ns"] == 5 and p["smem_bytes"] > cap
+    rc, p = plan(_clib.WGRAD, Shape(256, 256, 28, 28, 3, 3, 1, 1))
+    assert rc == 0 and p["ns"] == 2 and p["smem_bytes"] <= cap
+    rc, p = plan(_clib.WGRAD, Shape(256, 256, 28, 28, 3, 3, 1, 1), {"ns": 3})
+    assert rc == 0 and p["ns"] == 3 and p["smem_bytes"] > cap
+    # three slots of the 14 x 14 forward plan do not fit under the cap: the floor wins
+    rc, p = plan(_clib.FPROP, Shape(256, 512, 14, 14, 3, 3, 1, 1))
+    assert rc == 0 and p["ns"] == 3 and p["smem_bytes"] > cap
