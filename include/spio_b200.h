@@ -108,12 +108,75 @@ int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, c
                              const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes,
                              void* stream, void* dw_ready);
 
+/* spio_conv2d_gw8_backward with options (NULL = none).
+ *   dw_f16: dw points to fp16 [K][R][S][8] and receives the fp32 sums rounded once -- the
+ *     parameter's own type, which saves the cast autograd would otherwise launch after the
+ *     reference's fp32 grad_weight (spio/functional/conv2d_gw8_function.py:127).
+ *   *_function: CUfunction handles of kernels compiled just in time for the given tunes
+ *     (see the just-in-time section below); NULL = the variant built into the library.  They are
+ *     launched with cuLaunchKernelEx and the same programmatic-dependent-launch attribute, so a
+ *     just-in-time kernel takes part in the chain like a built-in one.  With dbias the
+ *     weight-gradient kernel must be the instantiation that also sums dy
+ *     (wgrad_dbias_function).
+ *   dp: after the reduce step this rank's dw (and dbias) are stored into every rank's exchange
+ *     buffer while the input-gradient kernel runs, and a last small kernel overwrites dw (dbias)
+ *     with the sum over the ranks, added in rank order (bit-identical on all ranks).  dw must be
+ *     fp32.  `dw_ready`, if given, is then recorded after that sum. */
+struct spio_dp_exchange;
+typedef struct spio_gw8_backward_opts {
+  int dw_f16;
+  void* wgrad_function;
+  void* wgrad_dbias_function;
+  void* dgrad_function;
+  const struct spio_dp_exchange* dp; /* data-parallel sum of dw (and dbias) over the GPUs of the
+                                        node, see below; NULL = single GPU */
+} spio_gw8_backward_opts;
+int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x, const void* dy, const void* w,
+                                const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
+                                const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes,
+                                void* stream, void* dw_ready, const spio_gw8_backward_opts* opts);
+
+/* ---- data-parallel sum of the weight gradient ----------------------------------------
+ * The path shards by batch (one process per GPU); its only exchange is the sum of the per-rank
+ * weight (and bias) gradients, a few thousand floats.  Instead of a host-issued all-reduce the
+ * sum runs as two small kernels inside the step's chain of dependent launches: spio_dp_push
+ * stores the rank's vector [a | b] into slot [rank] of EVERY rank's exchange buffer (plain
+ * peer stores over NVLink, then a system-wide fence and a flag), spio_dp_sum waits (bounded:
+ * SPIO_STATUS_PEER_TIMEOUT) for all ranks' flags of this exchange and overwrites [a | b] with
+ * the slots added in rank order.  Remote data always lands in local memory before it is used;
+ * nothing loads from a peer, and no TMA or multicast touches peer memory.  The reference has no
+ * multi-device support (its kernel cache is merely keyed by device ordinal,
+ * spio/kernels/kernel_key.py:13-18); a trainer would otherwise call torch.distributed.all_reduce
+ * on grad_weight after spio/functional/conv2d_gw8_function.py:147.
+ *
+ * Set-up, once: every rank allocates a buffer of spio_dp_buffer_bytes(world, capacity) with
+ * spio_dp_buffer_alloc (zero-filled; returns a 64-byte CUDA IPC handle), the ranks exchange the
+ * handles by any means (torch.distributed.all_gather_object, say) and open each other's with
+ * spio_dp_buffer_open.  `buffers[r]` is rank r's buffer as mapped in THIS process
+ * (buffers[rank] = the local one).  `seq` counts exchanges, starts at 0, is the same on all
+ * ranks and is incremented by the caller after every push + sum pair; every rank must take part
+ * in every exchange.  n_a and n_b are multiples of 4 floats, n_a + n_b <= capacity. */
+enum { SPIO_DP_MAX_WORLD = 16, SPIO_DP_IPC_HANDLE_BYTES = 64 };
+typedef struct spio_dp_exchange {
+  void* const* buffers;
+  int rank, world;
+  unsigned seq;
+  size_t capacity; /* floats per slot */
+} spio_dp_exchange;
+size_t spio_dp_buffer_bytes(int world, size_t capacity);
+int spio_dp_buffer_alloc(size_t bytes, void** buffer, void* ipc_handle /* 64 bytes out, or NULL */);
+int spio_dp_buffer_open(const void* ipc_handle, void** peer_buffer);
+int spio_dp_buffer_close(void* peer_buffer);
+int spio_dp_buffer_free(void* buffer);
+int spio_dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b, void* stream);
+int spio_dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, void* stream);
+
 /* Weight gradient for callers that must not allocate device memory.  It has no counterpart
  * in the reference.  Some callers cannot call cudaMalloc at the point where they need the
  * gradient: code running inside another framework's memory pool with a fixed budget, a
  * real-time loop that may not block on the allocator, a plugin that is handed tensors but no
  * allocator.  This variant does the same computation as spio_conv2d_gw8_wgrad but takes its
- * scratch from an 4 MiB buffer built into the library image (each GPU that loads the library
+ * scratch from a 4 MiB buffer built into the library image (each GPU that loads the library
  * holds those 4 MiB until the process exits), so the caller passes only inputs and output.
  *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *  - Shapes whose plan needs more than 4 MiB of scratch (3x3 filters on a 148-SM part need
@@ -180,6 +243,28 @@ int spio_function_set_max_dynamic_smem(void* function, int bytes);
 int spio_function_get_attribute(void* function, int which, int* value);
 /* args: one pointer per kernel parameter, as for cuLaunchKernel */
 int spio_function_launch(void* function, int grid, int block, int smem_bytes, void* stream, void** args);
+/* The same through cuLaunchKernelEx.  SPIO_LAUNCH_PROGRAMMATIC adds the programmatic-stream-
+ * serialization attribute: the kernel may become resident while its predecessor in the stream
+ * drains, so it MUST execute griddepcontrol.wait before it touches memory that predecessor
+ * writes (every gw8 kernel of this library does). */
+enum { SPIO_LAUNCH_PROGRAMMATIC = 1 };
+int spio_function_launch_ex(void* function, int grid, int block, int smem_bytes, void* stream, void** args,
+                            int flags);
+
+/* Launch of a gw8 kernel compiled just in time (`function`, a CUfunction from
+ * spio_module_get_function) for tune->wpg, tpw, pps (or tune->engine = 2): planning, tensor maps,
+ * the dynamic-tail counters and programmatic dependent launch are handled exactly as for the
+ * built-in variants, and the weight-gradient call is followed by the library's reduce kernel.
+ * These replace Kernel.launch -> Function.launch of the reference for its NVRTC-compiled kernels
+ * (spio/kernels/kernel.py:135-154, spio/cuda/driver.pyx:171-208). */
+int spio_conv2d_gw8_fprop_jit(void* function, void* y, const void* x, const void* w, const float* bias,
+                              const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* stream);
+int spio_conv2d_gw8_dgrad_jit(void* function, void* dx, const void* dy, const void* w,
+                              const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* stream);
+int spio_conv2d_gw8_wgrad_jit(void* function, float* dw, const void* x, const void* dy,
+                              const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* scratch,
+                              size_t scratch_bytes, void* stream);
+size_t spio_conv2d_gw8_wgrad_scratch_bytes_jit(const spio_gw8_shape* shape, const spio_gw8_tune* tune);
 
 /* Everything a just-in-time compiled gw8 kernel needs for one launch: the two tensor maps
  * and the geometry it takes by value, the launch dimensions and the status word.  Kernel
@@ -199,7 +284,9 @@ typedef struct spio_gw8_launch {
   int* status;
 } spio_gw8_launch;
 /* tune->wpg, tpw, pps must be given (or tune->engine = 2); they need not be a compiled variant.  plan_jit is the
- * host-only planner for such a configuration (cf. spio_conv2d_gw8_plan_for). */
+ * host-only planner for such a configuration (cf. spio_conv2d_gw8_plan_for).  prepare_launch serves callers that
+ * launch the function themselves (spio_function_launch); such a launch splits its work statically (no dynamic
+ * tail), because the counters of the dynamic tail are handed out per stream by the library's own launches. */
 int spio_conv2d_gw8_plan_jit(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, int sm_count,
                              int smem_optin_bytes, spio_gw8_plan_info* info);
 int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
@@ -227,10 +314,16 @@ int spio_layernorm_2d_bwd(void* dx, float* dweight, float* dbias, const void* dy
 int spio_conv2d_gw8_num_variants(void);
 int spio_conv2d_gw8_variant(int i, int* r, int* s, int* wpg, int* tpw, int* pps);
 
-/* Kernels record a bounded wait that gave up in a per-device status word.  This call
+/* Kernels record a bounded wait that gave up in a per-device status word
+ * (SPIO_STATUS_WAIT_TIMEOUT: an mbarrier wait inside a convolution kernel;
+ * SPIO_STATUS_PEER_TIMEOUT: the data-parallel exchange waited in vain for a peer).  This call
  * synchronises the current device, returns the word through *status (0 = ok) and clears
  * it.  Corresponds to the reference's error path in spio/cuda/driver.pyx:118-123. */
+enum { SPIO_STATUS_OK = 0, SPIO_STATUS_WAIT_TIMEOUT = 1, SPIO_STATUS_PEER_TIMEOUT = 2 };
 int spio_b200_device_status(int* status);
+/* Device address of that word on the current device (an int), for kernels written against
+ * the package's headers, whose last parameter it is. */
+int spio_b200_status_address(void** address);
 
 /* Message of the last failure on this thread ("" if none). */
 const char* spio_b200_last_error(void);

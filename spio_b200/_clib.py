@@ -44,6 +44,20 @@ class PlanInfo(Structure):
         return {name: getattr(self, name) for name, _ in self._fields_}
 
 
+class DpExchange(Structure):
+    """struct spio_dp_exchange."""
+
+    _fields_ = [("buffers", POINTER(c_void_p)), ("rank", c_int), ("world", c_int), ("seq", ctypes.c_uint),
+                ("capacity", c_size_t)]
+
+
+class BackwardOpts(Structure):
+    """struct spio_gw8_backward_opts."""
+
+    _fields_ = [("dw_f16", c_int), ("wgrad_function", c_void_p), ("wgrad_dbias_function", c_void_p),
+                ("dgrad_function", c_void_p), ("dp", POINTER(DpExchange))]
+
+
 class Launch(Structure):
     """struct spio_gw8_launch: tensor maps, geometry and launch dimensions of one call of a
     just-in-time compiled kernel."""
@@ -74,6 +88,25 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), POINTER(Tune),
          c_void_p, c_size_t, c_void_p, c_void_p]),
+    "spio_conv2d_gw8_backward_ex": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), POINTER(Tune),
+         c_void_p, c_size_t, c_void_p, c_void_p, POINTER(BackwardOpts)]),
+    "spio_conv2d_gw8_fprop_jit": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
+    "spio_conv2d_gw8_dgrad_jit": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
+    "spio_conv2d_gw8_wgrad_jit": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p, c_size_t, c_void_p]),
+    "spio_conv2d_gw8_wgrad_scratch_bytes_jit": (c_size_t, [POINTER(Shape), POINTER(Tune)]),
+    "spio_dp_buffer_bytes": (c_size_t, [c_int, c_size_t]),
+    "spio_dp_buffer_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_void_p]),
+    "spio_dp_buffer_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "spio_dp_buffer_close": (c_int, [c_void_p]),
+    "spio_dp_buffer_free": (c_int, [c_void_p]),
+    "spio_dp_push": (c_int, [POINTER(DpExchange), c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
+    "spio_dp_sum": (c_int, [POINTER(DpExchange), c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
     "spio_conv2d_gw8_wgrad_static": (
         c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
     "spio_conv2d_gw8_fprop_host": (
@@ -100,6 +133,7 @@ SIGNATURES = {
     "spio_function_set_max_dynamic_smem": (c_int, [c_void_p, c_int]),
     "spio_function_get_attribute": (c_int, [c_void_p, c_int, POINTER(c_int)]),
     "spio_function_launch": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, POINTER(c_void_p)]),
+    "spio_function_launch_ex": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, POINTER(c_void_p), c_int]),
     "spio_conv2d_gw8_plan_jit": (
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),
     "spio_conv2d_gw8_prepare_launch": (
@@ -115,6 +149,7 @@ SIGNATURES = {
     "spio_conv2d_gw8_variant": (
         c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
     "spio_b200_device_status": (c_int, [POINTER(c_int)]),
+    "spio_b200_status_address": (c_int, [POINTER(c_void_p)]),
     "spio_b200_last_error": (c_char_p, []),
     "spio_b200_version": (c_char_p, []),
 }

@@ -47,6 +47,7 @@ def _sources():
     units.append((CSRC / "gw8_tc_inst.cu", OBJ_DIR / "gw8_tc_inst.o", []))
     units.append((CSRC / "jit_driver.cpp", OBJ_DIR / "jit_driver.o", []))
     units.append((CSRC / "layernorm_2d.cu", OBJ_DIR / "layernorm_2d.o", []))
+    units.append((CSRC / "dp_exchange.cu", OBJ_DIR / "dp_exchange.o", []))
     return units
 
 

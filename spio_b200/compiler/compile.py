@@ -54,6 +54,7 @@ def compile_cuda(
     src_name: Optional[str] = None,
     ptxas_verbose: bool = False,
     return_log: bool = False,
+    defines: Optional[Dict[str, object]] = None,
 ):
     """Compile ``src`` (a path, or the source text itself together with ``src_name``) and
     return the cubin as bytes, or ``(cubin, log)`` with ``return_log``.
@@ -78,6 +79,8 @@ def compile_cuda(
         options.append("-default-device")
     if ptxas_verbose:
         options.append("--ptxas-options=-v")
+    for macro, value in (defines or {}).items():
+        options.append(f"-D{macro}" if value is None else f"-D{macro}={value}")
     options += [f"-I{path}" for path in (includes or []) + [cuda_include_dir()]]
 
     header_dict = header_dict or {}

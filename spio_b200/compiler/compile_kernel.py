@@ -47,6 +47,12 @@ extern "C" __global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
        float* __restrict__ scratch, int ns, int* __restrict__ status) {{
   conv2d_gw8_wgrad_body<Cfg>(x_map, dy_map, g, scratch, ns, status);
 }}
+// the instantiation that also sums dy for the bias gradient (odd number of filter taps)
+extern "C" __global__ void __launch_bounds__(Cfg::WGRAD_THREADS, 1)
+{name}__dbias(const __grid_constant__ TensorMap x_map, const __grid_constant__ TensorMap dy_map, const Gw8Geom g,
+       float* __restrict__ scratch, int ns, int* __restrict__ status) {{
+  conv2d_gw8_wgrad_body<Cfg, true>(x_map, dy_map, g, scratch, ns, status);
+}}
 """
 
 
@@ -78,8 +84,11 @@ def compile_kernel(
     lineinfo: bool = False,
     max_registers: Optional[int] = None,
     return_log: bool = False,
+    defines: Optional[Dict[str, object]] = None,
 ):
-    """Compile kernel source text against the package's kernel headers; returns the cubin."""
+    """Compile kernel source text against the package's kernel headers; returns the cubin.
+    ``defines`` become ``-D`` options (for instance ``SPIO_WAIT_LIMIT_NS``, the bound of the
+    kernels' barrier waits)."""
     assert arch is not None, "Must specify GPU architecture for kernel compilation."
     if isinstance(arch, tuple) and arch[0] < 10:
         raise ValueError("Minimum supported GPU compute capability is sm_100a (Blackwell B200).")
@@ -88,7 +97,7 @@ def compile_kernel(
     return compile_cuda(source, arch=arch, device_debug=debug, lineinfo=lineinfo, header_dict=headers,
                         max_registers=max_registers, src_name=source_name, ptxas_verbose=return_log,
                         default_device=True,  # the kernels' generic lambdas carry no __device__ mark
-                        return_log=return_log)
+                        return_log=return_log, defines=defines)
 
 
 def load_kernel(kernel_name: str, cubin: bytes, device_ordinal: int = 0):

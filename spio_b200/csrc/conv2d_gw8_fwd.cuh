@@ -255,17 +255,24 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
     // per-lane byte offset of each load instruction: the NQ shift-pair loads address one row,
     // the load of the odd last shift addresses both rows of a row pair
     // {row 0: px 0-7, px 8-15; row 1: px 0-7, px 8-15}
+    // The second 8-pixel half of a block tile lies 8 pixels further along the row, or, for
+    // images at most 8 pixels wide (g.pair_images), at the same place in the next image of the
+    // slot: ldmatrix and stmatrix take one row address per 8x8 matrix, so only these per-lane
+    // offsets differ between the two layouts.  Both distances are multiples of 1 KiB, which
+    // leaves the swizzle phase (pixel & 7) of an address unchanged.
+    const u32 half_in = g.pair_images ? g.img_in_bytes : 8u * 128u;
+    const u32 half_out = g.pair_images ? g.img_out_bytes : 8u * 128u;
     u32 ld_off[NLD];
 #pragma unroll
     for (int q = 0; q < NLD; ++q) {
       const u32 mi = (u32)lane >> 3;  // matrix this lane addresses
       const bool odd_col = ODD && q == NQ;
       const u32 sh = odd_col ? (u32)(S - 1) : (u32)(2 * q) + (mi >> 1);  // column shift
-      const u32 px = 8u * (mi & 1u) + sh + l7;                           // pixel within the block
+      const u32 px = sh + l7;                                            // pixel within its half
       const u32 row = odd_col ? (mi >> 1) : 0u;
-      ld_off[q] = (row * (u32)g.bw + px) * 128u + (((u32)grp ^ ((sh + l7) & 7u)) << 4);
+      ld_off[q] = (mi & 1u) * half_in + (row * (u32)g.bw + px) * 128u + (((u32)grp ^ (px & 7u)) << 4);
     }
-    const u32 st_off = (8u * (((u32)lane >> 3) & 1u) + l7) * 128u + (((u32)grp ^ l7) << 4);
+    const u32 st_off = (((u32)lane >> 3) & 1u) * half_out + l7 * 128u + (((u32)grp ^ l7) << 4);
     const u32 in_row_bytes = g.in_pair_bytes >> 1;        // bw * 128
     const u32 out_row_bytes = g.img_out_bytes >> 1;       // wt * 128
 
@@ -281,7 +288,10 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
       const int blk = tidx % g.nblk;
       int px0 = 16 * blk;
       if (px0 > g.wt - 16) px0 = g.wt - 16;  // the last block is shifted left, never past the tile
-      tile_code[t] = ((u32)(tidx / g.nblk) << 16) | ((u32)px0 * 128u);
+      if (g.pair_images)
+        tile_code[t] = (u32)(2 * tidx) << 16;  // images 2 * tidx and 2 * tidx + 1, pixels 0-7 of each
+      else
+        tile_code[t] = ((u32)(tidx / g.nblk) << 16) | ((u32)px0 * 128u);
     }
     auto in_off = [&](int t) { return (tile_code[t] & 0xffffu) + (tile_code[t] >> 16) * g.img_in_bytes; };
     auto out_off = [&](int t) { return (tile_code[t] & 0xffffu) + (tile_code[t] >> 16) * g.img_out_bytes; };

@@ -379,7 +379,8 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
   conv2d_gw8_wgrad_body<Cfg, WITH_BIAS>(x_map, dy_map, g, scratch, ns, status);
 }
 
-// dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c], and, when dbias
+// dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c] (fp32, or rounded once
+// to fp16 when dw_f16 is set: the parameter's own type, which saves autograd's cast), and, when dbias
 // is not NULL, dbias[k] = sum over parts of the bias sums behind it, added in a fixed order.
 // A block of 256 threads owns 8 float4 columns of a part; thread (cx, q) adds the parts q,
 // q+32, ... of column cx, then the 32 partial sums of a column are combined by two shuffle
@@ -387,8 +388,8 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
 // grid = ceil(n_chunks * GW8_PART_FLOATS(taps) / 4 / 8).
 template <int THREADS = 256>
 __global__ void __launch_bounds__(THREADS)
-conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, float* __restrict__ dbias,
-                               const float* __restrict__ scratch, int c, int taps, int n_parts) {
+conv2d_gw8_wgrad_reduce_kernel(void* __restrict__ dw, float* __restrict__ dbias,
+                               const float* __restrict__ scratch, int c, int taps, int n_parts, int dw_f16) {
   __shared__ float4 red[8][8];
   // Let an independent successor take SMs as they become free, then wait for the partials.
   grid_dependency_launch_dependents();
@@ -404,10 +405,16 @@ conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, float* __restrict__ dbias
   const int ck = col / chunk_f4;
   const int e = col - ck * chunk_f4;
   // where the column goes: a float4 of dw, a float4 of dbias, or nowhere (channels >= c)
+  // With dw_f16 the weight gradient is stored as fp16 (four values = 8 bytes per column); the
+  // bias gradient stays fp32.
   float4* out = nullptr;
+  uint2* out_h = nullptr;
   if (ck < n_chunks) {
     if (e < dw_f4) {
-      if (ck * 64 + e / (taps * 2) < c) out = reinterpret_cast<float4*>(dw) + (size_t)ck * dw_f4 + e;
+      if (ck * 64 + e / (taps * 2) < c) {
+        out = reinterpret_cast<float4*>(dw) + (size_t)ck * dw_f4 + e;
+        if (dw_f16) out_h = reinterpret_cast<uint2*>(dw) + (size_t)ck * dw_f4 + e;
+      }
     } else if (dbias != nullptr && ck * 64 + 4 * (e - dw_f4) < c) {
       out = reinterpret_cast<float4*>(dbias) + ck * 16 + (e - dw_f4);
     }
@@ -443,7 +450,12 @@ conv2d_gw8_wgrad_reduce_kernel(float* __restrict__ dw, float* __restrict__ dbias
       sum.z += v.z;
       sum.w += v.w;
     }
-    *out = sum;
+    if (out_h != nullptr) {
+      const __half2 lo = __floats2half2_rn(sum.x, sum.y), hi = __floats2half2_rn(sum.z, sum.w);
+      *out_h = make_uint2(*reinterpret_cast<const u32*>(&lo), *reinterpret_cast<const u32*>(&hi));
+    } else {
+      *out = sum;
+    }
   }
 }
 

@@ -34,6 +34,10 @@ int fail(const std::string& msg) {
 int jit_fail(const std::string& msg) { return fail(msg); }  // used by jit_driver.cpp
 namespace {
 
+}  // namespace
+bool gw8_pdl_enabled();
+namespace {
+
 int fail_cuda(const char* what, cudaError_t e) {
   return fail(std::string("CUDA error: ") + cudaGetErrorString(e) + " (" + what + ")");
 }
@@ -61,6 +65,7 @@ constexpr int kAlignSlack = 1024;      // dynamic shared memory is re-aligned to
 
 struct DeviceInfo {
   bool ready = false;
+  int dev = 0;
   int sms = 0;
   int smem_optin = 0;
   int* status = nullptr;
@@ -69,6 +74,28 @@ struct DeviceInfo {
 std::mutex g_mutex;
 DeviceInfo g_devices[kMaxDevices];
 std::vector<Gw8Variant> g_variants;
+
+// Counter pairs of the forward kernel's dynamic tail are owned per stream.  Kernels of one
+// stream that use the counters never overlap in their use of them: a launch touches them only
+// after it has waited for its predecessors (or, for the input-gradient kernel of the combined
+// backward call, after kernels that do not use them), and the last CTA clears them before the
+// grid completes.  Kernels of different streams may run at the same time, so they get different
+// pairs; a device that has used all pairs launches statically on further streams.
+struct SlotTable {
+  cudaStream_t streams[GW8_DYN_SLOTS];
+  int used = 0;
+};
+SlotTable g_slots[kMaxDevices];
+
+int slot_of_stream(int dev, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  SlotTable& t = g_slots[dev];
+  for (int i = 0; i < t.used; ++i)
+    if (t.streams[i] == stream) return i;
+  if (t.used == GW8_DYN_SLOTS) return -1;
+  t.streams[t.used] = stream;
+  return t.used++;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -149,11 +176,21 @@ int device_info(const DeviceInfo** out) {
       GW8_CUDA(cudaFuncSetAttribute(v.wgrad_bias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     d.smem_optin - kFwdStaticSmem));
     }
+    d.dev = dev;
     d.ready = true;
   }
   *out = &d;
   return 0;
 }
+
+}  // namespace
+int gw8_status_pointer(int** status) {
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;
+  *status = d->status;
+  return 0;
+}
+namespace {
 
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 inline int round_up(int a, int b) { return cdiv(a, b) * b; }
@@ -275,6 +312,15 @@ int make_plan_tc(int kind, const spio_gw8_shape* sh, const spio_gw8_tune& t, int
 // stops at this size while 3 (forward) or 2 (wgrad) slots remain; an explicit ns is taken as given.
 constexpr int kSmemSoftCap = 194 * 1024;
 
+// SPIO_PAIR_IMAGES=0 keeps the unpaired layout for images at most 8 pixels wide.
+bool pair_images_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SPIO_PAIR_IMAGES");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
 // Pairs per claim of the forward kernel's dynamic tail; SPIO_DYN=<n> changes it, SPIO_DYN=0
 // turns the dynamic tail off.
 int dyn_chunk_setting() {
@@ -346,23 +392,37 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
   const int avail = smem_optin - kFwdStaticSmem - kAlignSlack;
   const int qb = cdiv(g.out_w, 8);
 
+  // Forward kernel on images at most 8 pixels wide: a 16-pixel block tile would be half empty, so
+  // its two halves are given to two consecutive images of the slot (ncb = 1, nb even).  ncb = 2
+  // asks for the unpaired layout.
+  const bool pair = fwd && qb == 1 && sh->n >= 2 && t.ncb <= 1 && pair_images_enabled();
   int ncb = t.ncb ? t.ncb : 0;
-  if (ncb <= 0) {
-    const int n_ct0 = cdiv(tiles_needed(qb), max_tiles);
-    ncb = cdiv(qb, n_ct0);
-  }
-  if (ncb < min_ncb) ncb = min_ncb;
-  if (tiles_needed(ncb) > max_tiles) return fail("ncb exceeds the tile capacity of wpg * tpw");
   int nb = t.nb ? t.nb : 0;
-  if (nb <= 0) {
-    nb = 1;
-    if (ncb >= qb) {  // the whole width fits one column tile: batch images into a slot
-      nb = max_tiles / tiles_needed(ncb);
-      if (nb > sh->n) nb = sh->n;
-      if (nb < 1) nb = 1;
+  if (pair) {
+    ncb = 1;
+    if (nb <= 0) {
+      nb = 2 * max_tiles;
+      if (nb > sh->n) nb = sh->n & ~1;
     }
+    if (nb < 2 || (nb & 1) || nb > 2 * max_tiles)
+      return fail("paired images (ncb = 1) need an even nb of at most 2 * wpg * ceil(tpw / 2)");
+  } else {
+    if (ncb <= 0) {
+      const int n_ct0 = cdiv(tiles_needed(qb), max_tiles);
+      ncb = cdiv(qb, n_ct0);
+    }
+    if (ncb < min_ncb) ncb = min_ncb;
+    if (tiles_needed(ncb) > max_tiles) return fail("ncb exceeds the tile capacity of wpg * tpw");
+    if (nb <= 0) {
+      nb = 1;
+      if (ncb >= qb) {  // the whole width fits one column tile: batch images into a slot
+        nb = max_tiles / tiles_needed(ncb);
+        if (nb > sh->n) nb = sh->n;
+        if (nb < 1) nb = 1;
+      }
+    }
+    if (nb * tiles_needed(ncb) > max_tiles) return fail("nb * ncb exceeds the tile capacity of wpg * tpw");
   }
-  if (nb * tiles_needed(ncb) > max_tiles) return fail("nb * ncb exceeds the tile capacity of wpg * tpw");
 
   const int min_slots = 2;
   for (;;) {
@@ -392,14 +452,19 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
       ns = t.ns;
     }
     const bool box_ok = g.bw <= 256 && nb <= 256;
-    if (ns >= min_slots && box_ok && (t.nb || t.ncb || slot <= 48 * 1024 || (nb == 1 && ncb == min_ncb))) {
+    if (ns >= min_slots && box_ok &&
+        (t.nb || t.ncb || slot <= 48 * 1024 || (nb == (pair ? 2 : 1) && ncb == (pair ? 1 : min_ncb)))) {
       pl.ns = ns;
       pl.nob = nob;
       pl.smem = kAlignSlack + ns * (kind == SPIO_GW8_WGRAD ? slot + oslot : slot) + nob * oslot;
       break;
     }
     if (t.nb || t.ncb) return fail("requested tile does not fit in shared memory");
-    if (nb > 1)
+    if (pair && nb > 2)
+      nb = (nb / 2 + 1) & ~1;
+    else if (pair)
+      return fail("tile does not fit in shared memory");
+    else if (nb > 1)
       nb = nb / 2;
     else if (ncb > min_ncb)
       ncb = cdiv(ncb, 2) < min_ncb ? min_ncb : cdiv(ncb, 2);
@@ -407,7 +472,8 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
       return fail("tile does not fit in shared memory");
   }
   g.nblk = cdiv(g.wt, 16);
-  g.ntiles = g.nb * tiles_needed(g.ncb);
+  g.ntiles = pair ? g.nb / 2 : g.nb * tiles_needed(g.ncb);
+  g.pair_images = pair ? 1 : 0;
   g.in_pair_bytes = (unsigned)(2 * g.bw * 128);
   g.out_pair_bytes = (unsigned)(g.nb * 2 * g.wt * 128);
   g.slot_bytes = (unsigned)(g.nb * pps) * g.in_pair_bytes;
@@ -488,6 +554,9 @@ bool pdl_enabled() {
   }();
   return on;
 }
+}  // namespace
+bool gw8_pdl_enabled() { return pdl_enabled(); }
+namespace {
 
 // SPIO_L2_HINTS=0 turns the L2 eviction hints of the combined backward call off.
 bool l2_hints_enabled() {
@@ -516,88 +585,195 @@ int launch_kernel(const void* func, int grid, int threads, size_t smem, cudaStre
   return 0;
 }
 
+// The variant record of a kernel that is compiled just in time for (r, s, wpg, tpw, pps).
+int jit_variant(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, Gw8Variant* v) {
+  if (tune == nullptr) return fail("a just-in-time kernel needs a tile configuration");
+  if (kind < SPIO_GW8_FPROP || kind > SPIO_GW8_WGRAD) return fail("unknown kind");
+  if (tune->wpg < 1 || tune->wpg > 3 || tune->tpw < 1 || tune->tpw > 8 || tune->pps < 1 || tune->pps > 4)
+    return fail("a just-in-time kernel needs explicit wpg (1..3), tpw (1..8) and pps (1..4)");
+  if (check_shape(shape)) return 1;
+  *v = Gw8Variant{};
+  v->r = shape->r, v->s = shape->s, v->wpg = tune->wpg, v->tpw = tune->tpw, v->pps = tune->pps;
+  v->fwd_threads = (8 * tune->wpg + 4) * 32;
+  v->wgrad_threads = (8 * tune->wpg + 1) * 32;
+  return 0;
+}
+
+// A launch that repeats (same kind, shape, tuning, operand addresses, variant) reuses the plan
+// and the encoded tensor maps of the first time: both are pure functions of those values and of
+// the device's limits.  The cache is per host thread, direct-mapped; a collision just re-plans.
+struct LaunchKey {
+  int dev, kind, jit;
+  spio_gw8_shape sh;
+  spio_gw8_tune t;
+  const void* a;
+  const void* b;
+};
+struct LaunchEntry {
+  bool valid = false;
+  LaunchKey key;
+  Plan pl;
+  CUtensorMap m0, m1, m2;
+};
+constexpr int kLaunchCacheSize = 64;
+thread_local LaunchEntry g_launch_cache[kLaunchCacheSize];
+
+bool launch_cache_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SPIO_PLAN_CACHE");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+LaunchEntry* launch_cache_slot(const LaunchKey& key, bool* hit) {
+  const unsigned char* bytes = reinterpret_cast<const unsigned char*>(&key);
+  unsigned long long h = 1469598103934665603ull;
+  for (size_t i = 0; i < sizeof(LaunchKey); ++i) h = (h ^ bytes[i]) * 1099511628211ull;
+  LaunchEntry* e = &g_launch_cache[h % kLaunchCacheSize];
+  *hit = launch_cache_enabled() && e->valid && memcmp(&e->key, &key, sizeof(LaunchKey)) == 0;
+  return e;
+}
+
+void make_key(LaunchKey* key, int dev, int kind, bool jit, const spio_gw8_shape* sh, const spio_gw8_tune* tune,
+              const void* a, const void* b) {
+  memset(key, 0, sizeof *key);  // padding bytes take part in the comparison
+  key->dev = dev;
+  key->kind = kind;
+  key->jit = jit ? 1 : 0;
+  key->sh = *sh;
+  if (tune != nullptr) key->t = *tune;
+  key->a = a;
+  key->b = b;
+}
+
+// Plan and tensor maps of a forward / input-gradient launch (cached).
+int prepare_fwd(const DeviceInfo* d, int kind, void* out, const void* in, const spio_gw8_shape* sh,
+                const spio_gw8_tune* tune, bool jit, LaunchEntry** entry) {
+  if (sh == nullptr) return fail("shape is NULL");
+  LaunchKey key;
+  make_key(&key, d->dev, kind, jit, sh, tune, in, out);
+  bool hit = false;
+  LaunchEntry* e = launch_cache_slot(key, &hit);
+  *entry = e;
+  if (hit) return 0;
+  e->valid = false;
+  Gw8Variant v;
+  if (jit && jit_variant(kind, sh, tune, &v)) return 1;
+  if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &e->pl, jit ? &v : nullptr)) return 1;
+  const Gw8Geom& g = e->pl.g;
+  if (e->pl.engine == 2) {
+    if (encode_map(&e->m0, in, g.c, g.in_w, g.in_h, g.n, 64, 2, 1)) return 1;
+    if (encode_map(&e->m2, in, g.c, g.in_w, g.in_h, g.n, 64, 1, 1)) return 1;
+    if (encode_map(&e->m1, out, g.c, g.out_w, g.out_h, g.n, g.wt, 2, 1)) return 1;
+  } else {
+    const int pps = jit ? v.pps : e->pl.v->pps;
+    if (encode_map(&e->m0, in, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pps, g.nb)) return 1;
+    if (encode_map(&e->m1, out, g.c, g.out_w, g.out_h, g.n, g.wt, 2, g.nb)) return 1;
+  }
+  if (jit) e->pl.v = nullptr;  // the variant record lived on this stack frame
+  e->key = key;
+  e->valid = true;
+  return 0;
+}
+
+// jit_fn: a CUfunction compiled just in time for tune's (wpg, tpw, pps), or NULL for the variant
+// built into the library.
 int launch_fwd(int kind, void* out, const void* in, const void* w, const float* bias,
                const spio_gw8_shape* sh, const spio_gw8_tune* tune, cudaStream_t stream,
-               bool independent = false, int hint_in = L2_HINT_NONE) {
+               bool independent = false, int hint_in = L2_HINT_NONE, void* jit_fn = nullptr) {
   if (out == nullptr || in == nullptr || w == nullptr) return fail("NULL tensor pointer");
   const DeviceInfo* d = nullptr;
   if (device_info(&d)) return 1;
-  Plan pl;
-  if (make_plan(kind, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
-  pl.g.independent = (independent && pdl_enabled()) ? 1 : 0;
-  pl.g.hint_in = hint_in;
-  if (pl.g.dyn_chunk > 0) {
-    // A launch recorded into a CUDA graph would keep its counter slot for every replay, and two
-    // graphs holding the same slot could run at the same time: recorded launches stay static.
+  const bool jit = jit_fn != nullptr && !(tune != nullptr && tune->engine == 2);
+  LaunchEntry* e = nullptr;
+  if (prepare_fwd(d, kind, out, in, sh, tune, jit, &e)) return 1;
+  if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
+  const Plan& pl = e->pl;
+  Gw8Geom g = pl.g;
+  g.independent = (independent && pdl_enabled()) ? 1 : 0;
+  g.hint_in = hint_in;
+  if (g.dyn_chunk > 0) {
+    // A launch recorded into a CUDA graph may be replayed on any stream, beside anything: recorded
+    // launches stay static.  So do launches on streams beyond the number of counter pairs.
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
     GW8_CUDA(cudaStreamIsCapturing(stream, &capture));
-    if (capture != cudaStreamCaptureStatusNone) {
-      pl.g.dyn_chunk = 0;
-    } else {
-      static std::atomic<unsigned> next_slot{0};
-      pl.g.dyn_slot = (int)(next_slot.fetch_add(1) % GW8_DYN_SLOTS);
-    }
+    const int slot = capture != cudaStreamCaptureStatusNone ? -1 : slot_of_stream(d->dev, stream);
+    if (slot < 0)
+      g.dyn_chunk = 0;
+    else
+      g.dyn_slot = slot;
   }
-  if ((reinterpret_cast<size_t>(w) & 15u) != 0) return fail("weight pointer must be 16-byte aligned");
-  if (pl.engine == 2) {
-    const Gw8Geom& g = pl.g;
-    CUtensorMap in_map, row_map, out_map;
-    if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, 64, 2, 1)) return 1;
-    if (encode_map(&row_map, in, g.c, g.in_w, g.in_h, g.n, 64, 1, 1)) return 1;
-    if (encode_map(&out_map, out, g.c, g.out_w, g.out_h, g.n, g.wt, 2, 1)) return 1;
-    const __half* wp = static_cast<const __half*>(w);
-    int ns = pl.ns, nob = pl.nob;
-    int* status = d->status;
-    void* args[] = {&in_map, &row_map, &out_map, (void*)&g, &wp, &bias, &ns, &nob, &status};
-    return launch_kernel(pl.tc_kernel, pl.grid, pl.threads, pl.smem, stream, args);
-  }
-  const Gw8Geom& g = pl.g;
-  CUtensorMap in_map, out_map;
-  if (encode_map(&in_map, in, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
-  if (encode_map(&out_map, out, g.c, g.out_w, g.out_h, g.n, g.wt, 2, g.nb)) return 1;
   const __half* wp = static_cast<const __half*>(w);
   int ns = pl.ns, nob = pl.nob;
   int* status = d->status;
-  void* args[] = {&in_map, &out_map, (void*)&g, &wp, &bias, &ns, &nob, &status};
+  if (pl.engine == 2) {
+    void* args[] = {&e->m0, &e->m2, &e->m1, (void*)&g, &wp, &bias, &ns, &nob, &status};
+    if (jit_fn != nullptr) return jit_launch(jit_fn, pl.grid, pl.threads, pl.smem, stream, args, pdl_enabled());
+    return launch_kernel(pl.tc_kernel, pl.grid, pl.threads, pl.smem, stream, args);
+  }
+  void* args[] = {&e->m0, &e->m1, (void*)&g, &wp, &bias, &ns, &nob, &status};
+  if (jit) return jit_launch(jit_fn, pl.grid, pl.threads, pl.smem, stream, args, pdl_enabled());
   return launch_kernel(pl.v->fwd_kernel, pl.grid, pl.threads, pl.smem, stream, args);
 }
 
-int launch_reduce(float* dw, float* dbias, const float* scratch, int c, int taps, int n_parts,
-                  cudaStream_t stream) {
+int launch_reduce(void* dw, float* dbias, const float* scratch, int c, int taps, int n_parts,
+                  cudaStream_t stream, int dw_f16 = 0) {
   if (dbias != nullptr && taps % 2 == 0)
     return fail("the fused bias gradient needs an odd number of filter taps (r * s)");
   if ((reinterpret_cast<size_t>(dbias) & 15u) != 0) return fail("dbias must be 16-byte aligned");
   const int total_f4 = cdiv(c, 64) * (GW8_PART_FLOATS(taps) / 4);
-  void* args[] = {&dw, &dbias, &scratch, &c, &taps, &n_parts};
+  void* args[] = {&dw, &dbias, &scratch, &c, &taps, &n_parts, &dw_f16};
   return launch_kernel(reinterpret_cast<const void*>(&conv2d_gw8_wgrad_reduce_kernel<256>), cdiv(total_f4, 8), 256,
                        0, stream, args);
 }
 
-int launch_wgrad(float* dw, const void* x, const void* dy, const spio_gw8_shape* sh,
+// jit_fn: as for launch_fwd; with dbias it must be the instantiation that also sums dy.
+// dw_f16: dw points to fp16 and receives the fp32 sums rounded once.
+int launch_wgrad(void* dw, const void* x, const void* dy, const spio_gw8_shape* sh,
                  const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes,
                  cudaStream_t stream, int hint_x = L2_HINT_NONE, int hint_dy = L2_HINT_NONE,
-                 float* dbias = nullptr) {
+                 float* dbias = nullptr, void* jit_fn = nullptr, int dw_f16 = 0) {
   if (dw == nullptr || x == nullptr || dy == nullptr) return fail("NULL tensor pointer");
+  if (sh == nullptr) return fail("shape is NULL");
   const DeviceInfo* d = nullptr;
   if (device_info(&d)) return 1;
-  Plan pl;
-  if (make_plan(SPIO_GW8_WGRAD, sh, tune, d->sms, d->smem_optin, g_variants, &pl)) return 1;
+  const bool jit = jit_fn != nullptr;
+  LaunchKey key;
+  make_key(&key, d->dev, SPIO_GW8_WGRAD, jit, sh, tune, x, dy);
+  bool hit = false;
+  LaunchEntry* e = launch_cache_slot(key, &hit);
+  if (!hit) {
+    e->valid = false;
+    Gw8Variant v;
+    if (jit && jit_variant(SPIO_GW8_WGRAD, sh, tune, &v)) return 1;
+    if (make_plan(SPIO_GW8_WGRAD, sh, tune, d->sms, d->smem_optin, g_variants, &e->pl, jit ? &v : nullptr)) return 1;
+    const Gw8Geom& g = e->pl.g;
+    const int pps = jit ? v.pps : e->pl.v->pps;
+    if (encode_map(&e->m0, x, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pps, g.nb)) return 1;
+    if (encode_map(&e->m1, dy, g.c, g.out_w, g.out_h, g.n, g.wt, 2 * pps, g.nb)) return 1;
+    if (jit) e->pl.v = nullptr;
+    e->key = key;
+    e->valid = true;
+  }
+  const Plan& pl = e->pl;
   if (scratch == nullptr || scratch_bytes < pl.scratch_bytes) return fail("wgrad scratch buffer is too small");
   if ((reinterpret_cast<size_t>(scratch) & 15u) != 0 || (reinterpret_cast<size_t>(dw) & 15u) != 0)
     return fail("dw and scratch must be 16-byte aligned");
-  pl.g.hint_in = hint_x;
-  pl.g.hint_tiled = hint_dy;
-  const Gw8Geom& g = pl.g;
-  CUtensorMap x_map, dy_map;
-  if (encode_map(&x_map, x, g.c, g.in_w, g.in_h, g.n, g.bw, 2 * pl.v->pps, g.nb)) return 1;
-  if (encode_map(&dy_map, dy, g.c, g.out_w, g.out_h, g.n, g.wt, 2 * pl.v->pps, g.nb)) return 1;
+  Gw8Geom g = pl.g;
+  g.hint_in = hint_x;
+  g.hint_tiled = hint_dy;
   float* sc = static_cast<float*>(scratch);
   int ns = pl.ns;
   int* status = d->status;
-  void* args[] = {&x_map, &dy_map, (void*)&g, &sc, &ns, &status};
-  const void* kernel = dbias != nullptr ? pl.v->wgrad_bias_kernel : pl.v->wgrad_kernel;
-  if (launch_kernel(kernel, pl.grid, pl.threads, pl.smem, stream, args)) return 1;
-  return launch_reduce(dw, dbias, sc, g.c, sh->r * sh->s, pl.n_parts, stream);
+  void* args[] = {&e->m0, &e->m1, (void*)&g, &sc, &ns, &status};
+  if (jit) {
+    if (jit_launch(jit_fn, pl.grid, pl.threads, pl.smem, stream, args, pdl_enabled())) return 1;
+  } else {
+    const void* kernel = dbias != nullptr ? pl.v->wgrad_bias_kernel : pl.v->wgrad_kernel;
+    if (launch_kernel(kernel, pl.grid, pl.threads, pl.smem, stream, args)) return 1;
+  }
+  return launch_reduce(dw, dbias, sc, g.c, sh->r * sh->s, pl.n_parts, stream, dw_f16);
 }
 
 // ---------------------------------------------------------------- host-buffer variants
@@ -697,14 +873,25 @@ int spio_conv2d_gw8_wgrad(float* dw, const void* x, const void* dy, const spio_g
   return launch_wgrad(dw, x, dy, shape, tune, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
-int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, const void* dy, const void* w,
-                             const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
-                             const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes, void* stream,
-                             void* dw_ready) {
+int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x, const void* dy, const void* w,
+                                const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
+                                const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes, void* stream,
+                                void* dw_ready, const spio_gw8_backward_opts* opts) {
   if (dx == nullptr && dw == nullptr) return fail("neither gradient was asked for");
   if (dbias != nullptr && dw == nullptr) return fail("the bias gradient is computed together with dw");
   if (dbias != nullptr && (shape == nullptr || (shape->r * shape->s) % 2 == 0))
     return fail("the fused bias gradient needs an odd number of filter taps (r * s)");
+  static const spio_gw8_backward_opts kNone = {0, nullptr, nullptr, nullptr, nullptr};
+  const spio_gw8_backward_opts& o = opts ? *opts : kNone;
+  if (o.dp != nullptr && (dw == nullptr || o.dw_f16))
+    return fail("the data-parallel exchange sums an fp32 dw");
+  const size_t dw_floats = shape ? (size_t)shape->c * 8 * shape->r * shape->s : 0;
+  const size_t db_floats = (shape && dbias != nullptr) ? (size_t)shape->c : 0;
+  if (o.dp != nullptr && db_floats % 4 != 0)
+    return fail("the data-parallel exchange of dbias needs a channel count that is a multiple of 4");
+  void* wgrad_fn = dbias != nullptr ? o.wgrad_dbias_function : o.wgrad_function;
+  if (dw != nullptr && dbias != nullptr && o.wgrad_function != nullptr && wgrad_fn == nullptr)
+    return fail("a just-in-time weight-gradient kernel needs its bias-summing instantiation for dbias");
   cudaStream_t st = (cudaStream_t)stream;
   // Both kernels read dy.  The weight-gradient kernel asks the L2 to keep dy and to let x go
   // first, so that the input-gradient kernel finds as much of dy in the cache as fits; that
@@ -712,15 +899,62 @@ int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, c
   const bool both = dx != nullptr && dw != nullptr && l2_hints_enabled();
   if (dw != nullptr && launch_wgrad(dw, x, dy, shape, wgrad_tune, scratch, scratch_bytes, st,
                                     both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE,
-                                    both ? L2_HINT_EVICT_LAST : L2_HINT_NONE, dbias))
+                                    both ? L2_HINT_EVICT_LAST : L2_HINT_NONE, dbias, wgrad_fn, o.dw_f16))
     return 1;
-  if (dw != nullptr && dw_ready != nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
+  // Data-parallel: this rank's dw (and dbias) go to every rank's exchange buffer while the
+  // input-gradient kernel runs; the sum over the ranks follows that kernel.  No event, no second
+  // stream: the chain of dependent launches stays intact.
+  if (o.dp != nullptr && dp_push(o.dp, static_cast<const float*>(dw), dw_floats, dbias, db_floats, st)) return 1;
+  if (dw != nullptr && dw_ready != nullptr && o.dp == nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
   // dgrad reads dy and w and writes dx; the weight-gradient kernels read x and dy and write
-  // scratch and dw.  Neither touches what the other writes, so dgrad need not wait for them.
+  // scratch and dw (the exchange reads dw and writes the exchange buffers).  Neither touches what
+  // the other writes, so dgrad need not wait for them.
   if (dx != nullptr && launch_fwd(SPIO_GW8_DGRAD, dx, dy, w, nullptr, shape, dgrad_tune, st, dw != nullptr,
-                                  both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE))
+                                  both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE, o.dgrad_function))
     return 1;
+  if (o.dp != nullptr) {
+    if (dp_sum(o.dp, static_cast<float*>(dw), dw_floats, dbias, db_floats, st)) return 1;
+    if (dw_ready != nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
+  }
   return 0;
+}
+
+int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, const void* dy, const void* w,
+                             const spio_gw8_shape* shape, const spio_gw8_tune* dgrad_tune,
+                             const spio_gw8_tune* wgrad_tune, void* scratch, size_t scratch_bytes, void* stream,
+                             void* dw_ready) {
+  return spio_conv2d_gw8_backward_ex(dx, dw, dbias, x, dy, w, shape, dgrad_tune, wgrad_tune, scratch, scratch_bytes,
+                                     stream, dw_ready, nullptr);
+}
+
+int spio_conv2d_gw8_fprop_jit(void* function, void* y, const void* x, const void* w, const float* bias,
+                              const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* stream) {
+  if (function == nullptr) return fail("NULL function");
+  return launch_fwd(SPIO_GW8_FPROP, y, x, w, bias, shape, tune, (cudaStream_t)stream, false, L2_HINT_NONE, function);
+}
+
+int spio_conv2d_gw8_dgrad_jit(void* function, void* dx, const void* dy, const void* w, const spio_gw8_shape* shape,
+                              const spio_gw8_tune* tune, void* stream) {
+  if (function == nullptr) return fail("NULL function");
+  return launch_fwd(SPIO_GW8_DGRAD, dx, dy, w, nullptr, shape, tune, (cudaStream_t)stream, false, L2_HINT_NONE,
+                    function);
+}
+
+int spio_conv2d_gw8_wgrad_jit(void* function, float* dw, const void* x, const void* dy, const spio_gw8_shape* shape,
+                              const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes, void* stream) {
+  if (function == nullptr) return fail("NULL function");
+  return launch_wgrad(dw, x, dy, shape, tune, scratch, scratch_bytes, (cudaStream_t)stream, L2_HINT_NONE,
+                      L2_HINT_NONE, nullptr, function);
+}
+
+size_t spio_conv2d_gw8_wgrad_scratch_bytes_jit(const spio_gw8_shape* shape, const spio_gw8_tune* tune) {
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 0;
+  Gw8Variant v;
+  if (jit_variant(SPIO_GW8_WGRAD, shape, tune, &v)) return 0;
+  Plan pl;
+  if (make_plan(SPIO_GW8_WGRAD, shape, tune, d->sms, d->smem_optin, g_variants, &pl, &v)) return 0;
+  return pl.scratch_bytes;
 }
 
 int spio_conv2d_gw8_wgrad_static(float* dw, const void* x, const void* dy,
@@ -887,20 +1121,6 @@ int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy, const s
   return 0;
 }
 
-// The variant record of a kernel that is compiled just in time for (r, s, wpg, tpw, pps).
-static int jit_variant(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, Gw8Variant* v) {
-  if (tune == nullptr) return fail("a just-in-time kernel needs a tile configuration");
-  if (kind < SPIO_GW8_FPROP || kind > SPIO_GW8_WGRAD) return fail("unknown kind");
-  if (tune->wpg < 1 || tune->wpg > 3 || tune->tpw < 1 || tune->tpw > 8 || tune->pps < 1 || tune->pps > 4)
-    return fail("a just-in-time kernel needs explicit wpg (1..3), tpw (1..8) and pps (1..4)");
-  if (check_shape(shape)) return 1;
-  *v = Gw8Variant{};
-  v->r = shape->r, v->s = shape->s, v->wpg = tune->wpg, v->tpw = tune->tpw, v->pps = tune->pps;
-  v->fwd_threads = (8 * tune->wpg + 4) * 32;
-  v->wgrad_threads = (8 * tune->wpg + 1) * 32;
-  return 0;
-}
-
 int spio_conv2d_gw8_plan_jit(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune, int sm_count,
                              int smem_optin_bytes, spio_gw8_plan_info* info) {
   if (info == nullptr) return fail("info is NULL");
@@ -943,6 +1163,9 @@ int spio_conv2d_gw8_prepare_launch(int kind, const spio_gw8_shape* shape, const 
                    kind == SPIO_GW8_WGRAD ? 2 * v.pps : 2, pl.g.nb))
       return 1;
   }
+  // A launch assembled by the caller has no counter pair of its own: its work is split statically.
+  pl.g.dyn_chunk = 0;
+  pl.g.dyn_begin = 0;
   const Gw8Geom& g = pl.g;
   memcpy(out->in_map, &a, sizeof a);
   memcpy(out->out_map, &b, sizeof b);
@@ -963,6 +1186,14 @@ int spio_conv2d_gw8_wgrad_reduce(float* dw, float* dbias, const float* scratch, 
   if (dw == nullptr || scratch == nullptr || c <= 0 || c % 8 || taps <= 0 || n_parts <= 0)
     return fail("bad argument");
   return launch_reduce(dw, dbias, scratch, c, taps, n_parts, (cudaStream_t)stream);
+}
+
+int spio_b200_status_address(void** address) {
+  if (address == nullptr) return fail("address is NULL");
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;
+  *address = d->status;
+  return 0;
 }
 
 int spio_conv2d_gw8_plan(int kind, const spio_gw8_shape* shape, const spio_gw8_tune* tune,
@@ -1022,6 +1253,6 @@ int spio_b200_device_status(int* status) {
 
 const char* spio_b200_last_error(void) { return g_last_error.c_str(); }
 
-const char* spio_b200_version(void) { return "spio_b200 0.1 (sm_100a)"; }
+const char* spio_b200_version(void) { return "spio_b200 0.2 (sm_100a)"; }
 
 }  // extern "C"

@@ -34,6 +34,7 @@ enum { GW8_DYN_SLOTS = 64 };
 enum Gw8Status {
   GW8_OK = 0,
   GW8_WAIT_TIMEOUT = 1,  // a bounded mbarrier wait gave up
+  GW8_PEER_TIMEOUT = 2,  // the data-parallel exchange waited in vain for a peer's contribution
 };
 
 // Launch-time geometry.  "in" is the streamed operand with a halo (x for fprop and
@@ -65,6 +66,9 @@ struct Gw8Geom {
   int dyn_slot;        // which pair of counters behind the status word this launch uses
   int hint_in;         // L2 eviction hint (L2_HINT_*) for loads of the streamed operand
   int hint_tiled;      // wgrad: the same for loads of dy
+  int pair_images;     // fprop/dgrad, images at most 8 pixels wide: the two 8-pixel halves of a
+                       // 16-pixel block tile are pixels 0-7 of two consecutive images of the slot
+                       // (wt = 8, nb even, ntiles = nb / 2)
   // byte sizes derived from the above (kept here so that the kernels read them from the
   // constant bank instead of holding them in registers); pps = row pairs per slot
   unsigned in_pair_bytes;    // 2 rows of one image of the streamed operand: 2*bw*128

@@ -6,6 +6,9 @@
 #include <cuda_runtime.h>
 
 #include <cstddef>
+#include <string>
+
+#include "../../include/spio_b200.h"
 
 #include "gw8_common.cuh"
 
@@ -38,6 +41,20 @@ int gw8_variants_r2(const Gw8Variant** out);
 int gw8_variants_r3(const Gw8Variant** out);
 int gw8_variants_r4(const Gw8Variant** out);
 int gw8_variants_r5(const Gw8Variant** out);
+
+// Shared by the translation units of the library (gw8_capi.cu).
+int jit_fail(const std::string& msg);  // sets the calling thread's last-error string, returns 1
+bool gw8_pdl_enabled();                // programmatic dependent launch (SPIO_PDL=0 turns it off)
+int gw8_status_pointer(int** status);  // device address of the current device's status word
+
+// The data-parallel exchange of the weight gradient (dp_exchange.cu).
+int dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b,
+            cudaStream_t stream);
+int dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, cudaStream_t stream);
+
+// Driver-API launch of a just-in-time compiled function (jit_driver.cpp).
+int jit_launch(void* function, int grid, int block, int smem_bytes, cudaStream_t stream, void** args,
+               bool programmatic);
 
 // conv2d_gw8_fwd_tc_kernel<Gw8TcConfig<r, s>> for 1 <= r, s <= 3, else NULL.
 const void* gw8_tc_kernel(int r, int s);

@@ -14,6 +14,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -92,6 +93,7 @@ struct Driver {
   CUresult (*FuncGetAttribute)(int*, CUfunction_attribute, CUfunction) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                            CUstream, void**, void**) = nullptr;
+  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
 };
 Driver g_drv;
@@ -107,7 +109,10 @@ bool entry(const char* name, F& fn) {
   return true;
 }
 
+std::atomic<bool> g_drv_ready{false};
+
 int load_driver() {
+  if (g_drv_ready.load(std::memory_order_acquire)) return 0;  // the usual case takes no lock
   std::lock_guard<std::mutex> lock(g_jit_mutex);
   if (g_drv.ready) return 0;
   int dev = 0;
@@ -119,10 +124,11 @@ int load_driver() {
                   entry("cuModuleGetFunction", d.ModuleGetFunction) &&
                   entry("cuFuncSetAttribute", d.FuncSetAttribute) &&
                   entry("cuFuncGetAttribute", d.FuncGetAttribute) && entry("cuLaunchKernel", d.LaunchKernel) &&
-                  entry("cuGetErrorString", d.GetErrorString);
+                  entry("cuLaunchKernelEx", d.LaunchKernelEx) && entry("cuGetErrorString", d.GetErrorString);
   if (!ok) return jit_fail("CUDA error: a driver entry point is not available");
   d.ready = true;
   g_drv = d;
+  g_drv_ready.store(true, std::memory_order_release);
   return 0;
 }
 
@@ -141,6 +147,35 @@ int bind_context() {
 }
 
 }  // namespace
+
+namespace spio_b200 {
+
+// cuLaunchKernelEx on the caller's stream, optionally with the programmatic-stream-serialization
+// attribute the kernels built into the library are launched with, so that a just-in-time kernel
+// takes part in a chain of dependent launches like any other (the reference launches with plain
+// cuLaunchKernel on the NULL stream, spio/cuda/driver.pyx:200-208).
+int jit_launch(void* function, int grid, int block, int smem_bytes, cudaStream_t stream, void** args,
+               bool programmatic) {
+  if (function == nullptr) return jit_fail("NULL function");
+  if (grid <= 0 || block <= 0 || block > 1024) return jit_fail("bad launch dimensions");
+  if (load_driver()) return 1;
+  CUlaunchConfig cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDimX = (unsigned)grid, cfg.gridDimY = 1, cfg.gridDimZ = 1;
+  cfg.blockDimX = (unsigned)block, cfg.blockDimY = 1, cfg.blockDimZ = 1;
+  cfg.sharedMemBytes = (unsigned)smem_bytes;
+  cfg.hStream = static_cast<CUstream>(stream);
+  CUlaunchAttribute attr[1];
+  memset(attr, 0, sizeof attr);
+  attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+  attr[0].value.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic ? 1 : 0;
+  const CUresult r = g_drv.LaunchKernelEx(&cfg, static_cast<CUfunction>(function), args, nullptr);
+  return r == CUDA_SUCCESS ? 0 : drv_fail("cuLaunchKernelEx", r);
+}
+
+}  // namespace spio_b200
 
 extern "C" {
 
@@ -260,6 +295,13 @@ int spio_function_launch(void* function, int grid, int block, int smem_bytes, vo
   const CUresult r = g_drv.LaunchKernel(static_cast<CUfunction>(function), (unsigned)grid, 1, 1, (unsigned)block,
                                         1, 1, (unsigned)smem_bytes, static_cast<CUstream>(stream), args, nullptr);
   return r == CUDA_SUCCESS ? 0 : drv_fail("cuLaunchKernel", r);
+}
+
+int spio_function_launch_ex(void* function, int grid, int block, int smem_bytes, void* stream, void** args,
+                            int flags) {
+  if (bind_context()) return 1;
+  return spio_b200::jit_launch(function, grid, block, smem_bytes, static_cast<cudaStream_t>(stream), args,
+                               (flags & SPIO_LAUNCH_PROGRAMMATIC) != 0);
 }
 
 }  // extern "C"

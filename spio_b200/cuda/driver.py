@@ -104,7 +104,11 @@ class Function:
             return arg
         raise ValueError(f"unsupported kernel argument type {type(arg).__name__}")
 
-    def launch(self, grid, block, args, shared_mem_bytes: int = 0, stream: Optional[int] = None) -> None:
+    def launch(self, grid, block, args, shared_mem_bytes: int = 0, stream: Optional[int] = None,
+               programmatic: bool = False) -> None:
+        """``programmatic=True`` launches through cuLaunchKernelEx with the programmatic-stream-
+        serialization attribute; only for kernels that execute ``griddepcontrol.wait`` before they
+        touch memory written by their predecessor in the stream."""
         import ctypes
 
         import torch
@@ -124,8 +128,18 @@ class Function:
             pointers[i] = ctypes.addressof(v)
         if stream is None:
             stream = torch.cuda.current_stream().cuda_stream
-        _clib.check(_clib.load().spio_function_launch(self._handle, int(grid_x), int(block_x),
-                                                      int(shared_mem_bytes), stream, pointers), self.name)
+        lib = _clib.load()
+        if programmatic:
+            _clib.check(lib.spio_function_launch_ex(self._handle, int(grid_x), int(block_x), int(shared_mem_bytes),
+                                                    stream, pointers, 1), self.name)
+        else:
+            _clib.check(lib.spio_function_launch(self._handle, int(grid_x), int(block_x),
+                                                 int(shared_mem_bytes), stream, pointers), self.name)
+
+    @property
+    def handle(self) -> int:
+        """The CUfunction, as an integer, for the library's ``*_jit`` entry points."""
+        return self._handle
 
 
 class Module:

@@ -14,8 +14,27 @@ from typing import Optional, Tuple
 import torch
 
 from ..kernels import Conv2dGw8Params, conv2d_gw8_kernel_factory, conv2d_gw8_wgrad_kernel_factory
-from ..kernels.kernel import Kernel, launch_backward
+from ..kernels.kernel import launch_backward
 from ..util.tensor_format import to_channels_last
+
+
+# dtype of the grad_weight the backward operator returns.  float32 is the reference's contract
+# (spio/functional/conv2d_gw8_function.py:127); with float16 the reduce step of the weight-gradient
+# kernel rounds its fp32 sums once and stores the weight's own type, which saves the cast kernel
+# autograd launches to hand an fp16 parameter (or autocast's fp16 copy of it) its gradient.
+_grad_weight_dtype = torch.float32
+
+
+def set_grad_weight_dtype(dtype: torch.dtype) -> None:
+    """``torch.float32`` (default, as in the reference) or ``torch.float16``."""
+    global _grad_weight_dtype
+    if dtype not in (torch.float32, torch.float16):
+        raise ValueError("grad_weight dtype must be torch.float32 or torch.float16")
+    _grad_weight_dtype = dtype
+
+
+def get_grad_weight_dtype() -> torch.dtype:
+    return _grad_weight_dtype
 
 
 def _is_unit(value) -> bool:
@@ -99,7 +118,7 @@ def conv2d_gw8_backward_op(
     wgrad_kernel = dgrad_kernel = None
     if needs_weight_grad:
         # The kernel overwrites grad_weight, so no zero fill is needed.
-        grad_weight = torch.empty(params.weight_shape, device=inputs.device, dtype=torch.float32,
+        grad_weight = torch.empty(params.weight_shape, device=inputs.device, dtype=_grad_weight_dtype,
                                   memory_format=torch.channels_last)
         wgrad_kernel = conv2d_gw8_wgrad_kernel_factory.get_kernel(params, inputs.device)
     grad_input = _absent(inputs, torch.float16)
@@ -110,8 +129,7 @@ def conv2d_gw8_backward_op(
     # With an odd number of filter taps the weight-gradient kernel sums grad_output over
     # n, h, w in the unused half of its last MMA; otherwise torch does that reduction.
     grad_bias = _absent(inputs, torch.float32)
-    fused_bias = (needs_bias_grad and needs_weight_grad and (params.r * params.s) % 2 == 1
-                  and type(wgrad_kernel) is Kernel)
+    fused_bias = needs_bias_grad and needs_weight_grad and (params.r * params.s) % 2 == 1
     if needs_bias_grad:
         grad_bias = (torch.empty(params.k, device=inputs.device, dtype=torch.float32) if fused_bias
                      else grad_output.sum(dim=(0, 2, 3), dtype=torch.float32))
@@ -128,7 +146,7 @@ def conv2d_gw8_backward_op(
 @conv2d_gw8_backward_op.register_fake
 def _conv2d_gw8_backward_fake(inputs, weight, bias, _grad_output, _padding_y, _padding_x,
                               needs_input_grad, needs_weight_grad, needs_bias_grad):
-    grad_weight = (weight.new_empty(weight.shape, dtype=torch.float32)
+    grad_weight = (weight.new_empty(weight.shape, dtype=_grad_weight_dtype)
                    .to(memory_format=torch.channels_last) if needs_weight_grad
                    else _absent(inputs, torch.float32))
     grad_bias = (bias.new_empty(bias.shape, dtype=torch.float32) if needs_bias_grad

@@ -80,12 +80,20 @@ def enumerate_tiles(params, out_w: int, wpg: int, tpw: int, forward: bool = Fals
     1..4 column tiles; several images per slot
     only when one tile spans the whole width.  ncb counts 8-pixel column blocks.  The
     weight-gradient kernel holds wpg * tpw tiles of 8 pixels; the forward kernel holds
-    wpg * ceil(tpw / 2) blocks of 16 pixels and its column tile is at least 16 pixels wide."""
+    wpg * ceil(tpw / 2) blocks of 16 pixels and its column tile is at least 16 pixels wide, except
+    that images at most 8 pixels wide may be paired: ncb = 1 and an even nb put two images into
+    the two halves of every block."""
     max_tiles = wpg * ((tpw + 1) // 2) if forward else wpg * tpw
     need = (lambda ncb: divup(max(ncb, 2), 2)) if forward else (lambda ncb: ncb)
     col_blocks = divup(out_w, 8)
     seen = set()
     yield 0, 0  # always plannable: wide images with few tiles per warp need more column tiles than tried below
+    if forward and col_blocks == 1:
+        # images at most 8 pixels wide: two images share a 16-pixel block (ncb = 1, nb even)
+        nb = 2
+        while nb <= 2 * max_tiles and nb <= params.n:
+            yield 1, nb
+            nb *= 2
     for n_ct in range(1, 5):
         ncb = max(divup(col_blocks, n_ct), 2 if forward else 1)
         if need(ncb) > max_tiles or ncb in seen:

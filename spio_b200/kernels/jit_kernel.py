@@ -28,6 +28,7 @@ class JitKernel(Kernel):
         self.compile_log: str = ""
         self.module = None
         self.function = None
+        self.dbias_function = None  # weight gradient only: the instantiation that also sums dy
         self._arch = None
 
     # ------------------------------------------------------------ life cycle
@@ -91,6 +92,9 @@ class JitKernel(Kernel):
         self.module, self.function = load_kernel(self.function_name, self.cubin, device_ordinal)
         self._check_register_hand_over()
         self.function.set_max_dynamic_shared_memory_size(self.plan["smem_bytes"])
+        if self.kind == _clib.WGRAD:
+            self.dbias_function = self.module.get_function(self.function_name + "__dbias")
+            self.dbias_function.set_max_dynamic_shared_memory_size(self.plan["smem_bytes"])
         self._scratch_bytes = int(self.plan["scratch_bytes"])
         if clear_cubin:
             self.cubin = None
@@ -110,8 +114,17 @@ class JitKernel(Kernel):
             raise ValueError(f"Error in kernel {self}: allocated {launch} registers per thread; "
                              f"the register hand-over of the forward kernel does not fit")
 
+    @property
+    def function_handle(self):
+        return self.function.handle if self.function is not None else None
+
+    @property
+    def dbias_function_handle(self):
+        return self.dbias_function.handle if self.dbias_function is not None else None
+
     def unload(self) -> None:
         self.function = None
+        self.dbias_function = None
         if self.module is not None:
             self.module.unload()
             self.module = None
@@ -126,6 +139,9 @@ class JitKernel(Kernel):
 
     # ------------------------------------------------------------ launch
     def launch(self, *args) -> None:
+        """Same argument lists as :meth:`Kernel.launch`.  The library plans the launch, encodes (and
+        caches) the tensor maps and launches the function through cuLaunchKernelEx with the
+        programmatic-dependent-launch attribute, exactly as it does for its built-in variants."""
         if self.function is None:
             raise ValueError(f"Error in kernel {self}: kernel is not loaded")
         try:
@@ -133,27 +149,19 @@ class JitKernel(Kernel):
             dev = args[0].device
             with torch.cuda.device(dev):
                 stream = torch.cuda.current_stream(dev).cuda_stream
-                # fprop (y, x, w, bias), dgrad (dx, dy, w, None), wgrad (dw, x, dy):
-                # the streamed operand is args[1]; the tiled one is the result, or dy for wgrad
-                tiled = args[2] if self.kind == _clib.WGRAD else args[0]
-                lp = _clib.Launch()
-                _clib.check(self._lib.spio_conv2d_gw8_prepare_launch(
-                    self.kind, ctypes.byref(self._shape), self._tune_ref(), args[1].data_ptr(),
-                    tiled.data_ptr(), ctypes.byref(lp)))
-                status = ctypes.c_void_p(lp.status)
-                if self.kind == _clib.WGRAD:
-                    scratch = torch.empty(lp.scratch_bytes, dtype=torch.uint8, device=dev)
-                    kargs = [lp.in_map, lp.out_map, lp.geom, scratch, int(lp.ns), status]
+                ptr = [a.data_ptr() if a is not None else None for a in args]
+                sh, tn, fn = ctypes.byref(self._shape), self._tune_ref(), self.function.handle
+                if self.kind == _clib.FPROP:
+                    rc = self._lib.spio_conv2d_gw8_fprop_jit(fn, ptr[0], ptr[1], ptr[2], ptr[3], sh, tn, stream)
+                elif self.kind == _clib.DGRAD:
+                    rc = self._lib.spio_conv2d_gw8_dgrad_jit(fn, ptr[0], ptr[1], ptr[2], sh, tn, stream)
                 else:
-                    if args[2].data_ptr() % 16:
-                        raise ValueError("weight pointer must be 16-byte aligned")
-                    maps = [lp.in_map, lp.row_map, lp.out_map] if self._tune.engine == 2 else [lp.in_map, lp.out_map]
-                    kargs = maps + [lp.geom, args[2], args[3], int(lp.ns), int(lp.nob), status]
-                self.function.launch(lp.grid, lp.threads, kargs, shared_mem_bytes=lp.smem_bytes, stream=stream)
-                if self.kind == _clib.WGRAD:
-                    _clib.check(self._lib.spio_conv2d_gw8_wgrad_reduce(
-                        args[0].data_ptr(), None, scratch.data_ptr(), self.params.c, self.params.r * self.params.s,
-                        lp.n_parts, stream))
+                    from .kernel import scratch_for
+
+                    scratch = scratch_for(dev, stream, self._scratch_bytes)
+                    rc = self._lib.spio_conv2d_gw8_wgrad_jit(fn, ptr[0], ptr[1], ptr[2], sh, tn,
+                                                             scratch.data_ptr(), self._scratch_bytes, stream)
+                _clib.check(rc)
         except Exception as exc:
             raise ValueError(f"Error in kernel {self}: {exc}") from exc
 

@@ -36,6 +36,24 @@ def shape_of(params) -> _clib.Shape:
                        params.padding_h, params.padding_w)
 
 
+# Weight-gradient scratch, one buffer per (device, stream): kernels of one stream run in order (the
+# weight-gradient kernel never skips its dependency wait), so they can share it; kernels of
+# different streams cannot.  Buffers only grow; outgrown ones are kept alive because a recorded
+# CUDA graph may still hold their address.
+_scratch: dict = {}
+_outgrown: list = []
+
+
+def scratch_for(device, stream_ptr: int, nbytes: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _outgrown.append(buf)
+        buf = _scratch[key] = torch.empty(max(nbytes, 4 << 20), dtype=torch.uint8, device=device)
+    return buf
+
+
 class Kernel:
     def __init__(self, kernel_name: str, base_name: str, params, config=None,
                  args_checker=check_channels_last):
@@ -111,7 +129,7 @@ class Kernel:
                 elif self.kind == _clib.DGRAD:
                     rc = self._lib.spio_conv2d_gw8_dgrad(ptr[0], ptr[1], ptr[2], sh, tn, stream)
                 else:
-                    scratch = torch.empty(self._scratch_bytes, dtype=torch.uint8, device=dev)
+                    scratch = scratch_for(dev, stream, self._scratch_bytes)
                     rc = self._lib.spio_conv2d_gw8_wgrad(ptr[0], ptr[1], ptr[2], sh, tn,
                                                          scratch.data_ptr(), self._scratch_bytes, stream)
             _clib.check(rc)
@@ -127,33 +145,37 @@ class Kernel:
 def launch_backward(wgrad_kernel: Kernel, dgrad_kernel: Optional[Kernel], grad_input, grad_weight, inputs,
                     grad_output, weight, grad_bias=None) -> None:
     """Weight gradient, optionally the bias gradient (odd number of filter taps only) and,
-    with ``dgrad_kernel``, the input gradient of a layer.  Two ahead-of-time kernels go through the library's combined
-    entry point, which chains weight gradient, reduce and input gradient with programmatic
-    dependent launch; anything else (a just-in-time kernel) is launched one after the other."""
-    if type(wgrad_kernel) is not Kernel or (dgrad_kernel is not None and type(dgrad_kernel) is not Kernel):
-        if grad_bias is not None:
-            raise ValueError("the fused bias gradient needs the built-in weight-gradient kernel")
-        wgrad_kernel(grad_weight, inputs, grad_output)
-        if dgrad_kernel is not None:
-            dgrad_kernel(grad_input, grad_output, weight, None)
-        return
-    if wgrad_kernel._lib is None or (dgrad_kernel is not None and dgrad_kernel._lib is None):
-        raise ValueError(f"Error in kernel {wgrad_kernel}: kernel is not loaded")
+    with ``dgrad_kernel``, the input gradient of a layer, through the library's combined entry
+    point: weight gradient, reduce and input gradient are chained with programmatic dependent
+    launch.  Kernels built into the library and kernels compiled just in time mix freely; the
+    latter are passed by their function handles.  ``grad_weight`` may be fp32 (the reference's
+    contract) or fp16 (the parameter's own type, rounded once from the fp32 sum)."""
+    kernels = [wgrad_kernel] + ([dgrad_kernel] if dgrad_kernel is not None else [])
+    for k in kernels:
+        if k._lib is None:
+            raise ValueError(f"Error in kernel {k}: kernel is not loaded")
     try:
         wgrad_kernel._args_checker((grad_weight, inputs, grad_output))
         if dgrad_kernel is not None:
             dgrad_kernel._args_checker((grad_input, grad_output, weight, None))
+        if grad_weight.dtype not in (torch.float32, torch.float16):
+            raise ValueError("grad_weight must be float32 or float16")
         dev = inputs.device
         stream = torch.cuda.current_stream(dev).cuda_stream
         nbytes = wgrad_kernel._scratch_bytes
+        opts = _clib.BackwardOpts(
+            1 if grad_weight.dtype == torch.float16 else 0,
+            getattr(wgrad_kernel, "function_handle", None),
+            getattr(wgrad_kernel, "dbias_function_handle", None),
+            getattr(dgrad_kernel, "function_handle", None) if dgrad_kernel is not None else None)
         with torch.cuda.device(dev):
-            scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-            rc = wgrad_kernel._lib.spio_conv2d_gw8_backward(
+            scratch = scratch_for(dev, stream, nbytes)
+            rc = wgrad_kernel._lib.spio_conv2d_gw8_backward_ex(
                 grad_input.data_ptr() if dgrad_kernel is not None else None, grad_weight.data_ptr(),
                 grad_bias.data_ptr() if grad_bias is not None else None, inputs.data_ptr(),
                 grad_output.data_ptr(), weight.data_ptr(), ctypes.byref(wgrad_kernel._shape),
                 dgrad_kernel._tune_ref() if dgrad_kernel is not None else None,
-                wgrad_kernel._tune_ref(), scratch.data_ptr(), nbytes, stream, None)
+                wgrad_kernel._tune_ref(), scratch.data_ptr(), nbytes, stream, None, ctypes.byref(opts))
         _clib.check(rc)
     except Exception as exc:
         raise ValueError(f"Error in kernels {wgrad_kernel}, {dgrad_kernel}: {exc}") from exc

@@ -177,3 +177,53 @@ def test_step_is_capturable_in_a_cuda_graph():
         torch.cuda.synchronize()
         assert torch.equal(y, ref_y) and torch.equal(dx, ref_dx) and torch.equal(dw, ref_dw)
     assert capi.status() == 0
+
+
+@pytest.mark.parametrize("sh", [O.Shape(16, 64, 56, 56, 3, 3, 1, 1), O.Shape(6, 136, 14, 14, 5, 5, 2, 2),
+                                O.Shape(8, 768, 7, 7, 3, 3, 1, 1)], ids=str)
+def test_weight_gradient_in_the_parameters_own_type(sh):
+    """With ``dw_f16`` the reduce step stores the fp32 sums rounded once to fp16: exactly the
+    fp32 result passed through one round-to-nearest, which is what autograd's cast kernel would
+    have produced from the reference's fp32 grad_weight."""
+    import ctypes
+
+    from spio_b200 import _clib
+
+    x, w, _, dy = O.make_inputs(sh, seed=23, bias=False)
+    xd, wd, dyd = (capi.to_dev(t) for t in (x, w, dy))
+    lib = _clib.load()
+    s = capi.cshape(sh)
+    nbytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(ctypes.byref(s), None)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda:0")
+    dw16 = torch.full((sh.c, 8, sh.r, sh.s), capi.DEAD_VALUE, dtype=torch.float16, device="cuda:0")
+    dw16 = dw16.contiguous(memory_format=capi.CL)
+    db = torch.full((sh.c,), capi.DEAD_VALUE, dtype=torch.float32, device="cuda:0")
+    odd = (sh.r * sh.s) % 2 == 1
+    opts = _clib.BackwardOpts(1, None, None, None)
+    _clib.check(lib.spio_conv2d_gw8_backward_ex(
+        None, dw16.data_ptr(), db.data_ptr() if odd else None, xd.data_ptr(), dyd.data_ptr(), wd.data_ptr(),
+        ctypes.byref(s), None, None, scratch.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream, None,
+        ctypes.byref(opts)))
+    dw32 = capi.wgrad(xd, dyd, sh)
+    assert torch.equal(dw16, dw32.half())
+    if odd:
+        torch.testing.assert_close(db.cpu(), dy.float().sum(dim=(0, 2, 3)), rtol=1e-3, atol=5e-2)
+    assert capi.status() == 0
+
+
+def test_operator_returns_fp16_weight_gradient_when_asked():
+    from spio_b200.functional import conv2d_gw8_backward_op, get_grad_weight_dtype, set_grad_weight_dtype
+
+    sh = O.Shape(8, 64, 20, 20, 3, 3, 1, 1)
+    x, w, b, dy = O.make_inputs(sh, seed=29, bias=True)
+    xd, wd, bd, dyd = (capi.to_dev(t) for t in (x, w, b, dy))
+    assert get_grad_weight_dtype() == torch.float32
+    _, dw32, db32 = conv2d_gw8_backward_op(xd, wd, bd, dyd, 1, 1, False, True, True)
+    set_grad_weight_dtype(torch.float16)
+    try:
+        _, dw16, db16 = conv2d_gw8_backward_op(xd, wd, bd, dyd, 1, 1, False, True, True)
+    finally:
+        set_grad_weight_dtype(torch.float32)
+    assert dw32.dtype == torch.float32 and dw16.dtype == torch.float16
+    assert torch.equal(dw16, dw32.half()) and torch.equal(db16, db32)
+    assert capi.status() == 0

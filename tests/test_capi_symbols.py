@@ -55,8 +55,14 @@ def test_planner_respects_limits(case, kind):
     if kind == _clib.WGRAD:   # tiles of 8 pixels x 2 rows
         assert p["nb"] * p["ncb"] <= p["wpg"] * p["tpw"]
     else:                     # blocks of 16 pixels x 1 row, (tpw + 1) // 2 per warp
-        assert p["ncb"] >= 2
-        assert p["nb"] * ((p["ncb"] + 1) // 2) <= p["wpg"] * ((p["tpw"] + 1) // 2)
+        blocks = p["wpg"] * ((p["tpw"] + 1) // 2)
+        out_w8 = ((sh.w if kind == _clib.DGRAD else sh.q) + 7) // 8
+        if p["ncb"] == 1:     # images at most 8 pixels wide: two images share a block
+            assert out_w8 == 1 and sh.n >= 2
+            assert p["nb"] % 2 == 0 and p["nb"] // 2 <= blocks
+        else:
+            assert p["ncb"] >= 2
+            assert p["nb"] * ((p["ncb"] + 1) // 2) <= blocks
     assert p["ns"] >= 2 and p["pps"] in (1, 2)
     assert p["threads"] % 32 == 0 and p["threads"] <= 1024
     out_w = sh.w if kind == _clib.DGRAD else sh.q

@@ -71,27 +71,37 @@ def test_channel_resolution_ladder_reduced_batch(c, hw):
     check_all(O.Shape(4 if hw > 14 else 16, c, hw, hw, 3, 3, 1, 1), c in (96, 192, 384), seed=1236)
 
 
-def _every(configs, step):
-    configs = list(configs)
-    return configs[::step] if len(configs) > step else configs
-
-
 @pytest.mark.parametrize("params", [
     Conv2dGw8Params(n=4, c=64, h=16, w=32, padding=1, r=3, s=3, has_bias=True),
     Conv2dGw8Params(n=3, c=72, h=28, w=28, padding=1, r=3, s=3),
     Conv2dGw8Params(n=2, c=64, h=12, w=40, padding=(2, 1), r=5, s=3),
+    Conv2dGw8Params(n=6, c=72, h=7, w=7, padding=1, r=3, s=3, has_bias=True),
 ], ids=lambda p: p.encode())
 def test_every_tile_configuration(params):
-    """Each configuration of the kernel families' configuration spaces gives the same result."""
+    """EVERY configuration of the kernel families' configuration spaces gives the oracle's
+    result, as the reference's kernel tests run every configuration of a shape
+    (tests/test_conv2d_gw8.py:110-201).  The oracle runs once per shape."""
     attr = get_device_attributes(0)
     sh = O.Shape(params.n, params.c, params.h, params.w, params.r, params.s, params.padding_h,
                  params.padding_w)
-    for cfg in _every(conv2d_gw8_kernel_factory.configs(params, attr), 5):
-        check_all(sh, params.has_bias, tune=cfg.as_tune(), what=("fprop",))
-    for cfg in _every(conv2d_gw8_kernel_factory.configs(params, attr, igrad=True), 5):
-        check_all(sh, params.has_bias, tune=cfg.as_tune(), what=("dgrad",))
-    for cfg in _every(conv2d_gw8_wgrad_kernel_factory.configs(params, attr), 3):
-        check_all(sh, params.has_bias, tune=cfg.as_tune(), what=("wgrad",))
+    x, w, b, dy = O.make_inputs(sh, seed=11, bias=params.has_bias)
+    xd, wd, bd, dyd = (capi.to_dev(t) for t in (x, w, b, dy))
+    want_y, want_dx, want_dw = O.c_fprop(x, w, b, sh), O.c_dgrad(dy, w, sh), O.c_wgrad(x, dy, sh)
+    counts = []
+    configs = list(conv2d_gw8_kernel_factory.configs(params, attr))
+    counts.append(len(configs))
+    for cfg in configs:
+        O.assert_close(capi.fprop(xd, wd, bd, sh, cfg.as_tune()), want_y, sh, "fprop", f"{sh} {cfg}")
+    configs = list(conv2d_gw8_kernel_factory.configs(params, attr, igrad=True))
+    counts.append(len(configs))
+    for cfg in configs:
+        O.assert_close(capi.dgrad(dyd, wd, sh, cfg.as_tune()), want_dx, sh, "dgrad", f"{sh} {cfg}")
+    configs = list(conv2d_gw8_wgrad_kernel_factory.configs(params, attr))
+    counts.append(len(configs))
+    for cfg in configs:
+        O.assert_close(capi.wgrad(xd, dyd, sh, cfg.as_tune()), want_dw, sh, "wgrad", f"{sh} {cfg}")
+    assert min(counts) >= 20
+    assert capi.status() == 0
 
 
 @pytest.mark.parametrize("tune", [dict(grid=1), dict(grid=3), dict(grid=7, ns=2, nob=1),

@@ -165,3 +165,85 @@ def test_jit_tcgen05_kernel_is_bit_identical_to_the_built_in_one():
     O.assert_close(out[1][0], O.c_fprop(x, w, b, sh), sh, "fprop", "jit tcgen05")
     O.assert_close(out[1][1], O.c_dgrad(dy, w, sh), sh, "dgrad", "jit tcgen05")
     assert capi.status() == 0
+
+
+def test_jit_kernels_join_the_backward_chain_with_the_fused_bias_gradient():
+    """Just-in-time kernels go through the same combined backward call as the built-in ones
+    (cuLaunchKernelEx with the programmatic-dependent-launch attribute), including the
+    instantiation that sums dy for the bias gradient; a built-in variant compiled just in time
+    gives the built-in kernel's bits."""
+    from spio_b200.kernels.kernel import launch_backward
+
+    sh = O.Shape(24, 72, 28, 28, 3, 3, 1, 1)
+    x, w, b, dy = O.make_inputs(sh, seed=17, bias=True)
+    xd, wd, dyd = (capi.to_dev(t) for t in (x, w, dy))
+    p = params_of(sh, has_bias=True)
+    attr = get_device_attributes(0)
+    out = []
+    for jit in (False, True):
+        wk = conv2d_gw8_wgrad_kernel_factory.make_kernel(p, Conv2dGw8WgradConfig(wpg=2, tpw=4, pps=2), attr, jit=jit)
+        dk = conv2d_gw8_kernel_factory.make_kernel(p, Conv2dGw8Config(wpg=2, tpw=4, pps=2), attr, jit=jit, igrad=True)
+        for k in (wk, dk):
+            k.compile(attr)
+            k.load(0)
+            assert isinstance(k, JitKernel) == jit
+        dx = dead((sh.n, sh.c, sh.h, sh.w), torch.float16)
+        dw = dead((sh.c, 8, sh.r, sh.s), torch.float32)
+        db = torch.full((sh.c,), capi.DEAD_VALUE, dtype=torch.float32, device="cuda:0")
+        for _ in range(3):  # back to back: each call's kernels overlap the tail of the previous call's
+            launch_backward(wk, dk, dx, dw, xd, dyd, wd, db)
+        out.append((dx, dw, db))
+    for a, b2 in zip(out[0], out[1]):
+        assert torch.equal(a, b2)
+    O.assert_close(out[1][0], O.c_dgrad(dy, w, sh), sh, "dgrad", "jit chain")
+    O.assert_close(out[1][1], O.c_wgrad(x, dy, sh), sh, "wgrad", "jit chain")
+    torch.testing.assert_close(out[1][2].cpu(), dy.float().sum(dim=(0, 2, 3)), rtol=1e-3, atol=5e-2)
+    # a mixed chain: just-in-time weight gradient of a configuration that is not built in,
+    # built-in input gradient
+    wk = conv2d_gw8_wgrad_kernel_factory.make_kernel(p, Conv2dGw8WgradConfig(wpg=1, tpw=3, pps=1), attr)
+    wk.compile(attr)
+    wk.load(0)
+    assert isinstance(wk, JitKernel)
+    dk = conv2d_gw8_kernel_factory.make_kernel(p, Conv2dGw8Config(), attr, igrad=True)
+    dk.compile(attr)
+    dk.load(0)
+    dx2, dw2 = dead((sh.n, sh.c, sh.h, sh.w), torch.float16), dead((sh.c, 8, sh.r, sh.s), torch.float32)
+    db2 = torch.full((sh.c,), capi.DEAD_VALUE, dtype=torch.float32, device="cuda:0")
+    launch_backward(wk, dk, dx2, dw2, xd, dyd, wd, db2)
+    O.assert_close(dw2, O.c_wgrad(x, dy, sh), sh, "wgrad", "mixed chain")
+    torch.testing.assert_close(db2, out[0][2], rtol=1e-4, atol=1e-2)
+    assert torch.equal(dx2, capi.dgrad(dyd, wd, sh))
+    assert capi.status() == 0
+
+
+def test_jit_forward_kernel_replayed_from_a_cuda_graph():
+    """A just-in-time launch recorded into a CUDA graph splits its work statically (it owns no
+    dynamic-tail counters) and gives the bits of the live launch, replay after replay, also with
+    another stream running the same kernel live beside it."""
+    sh = O.Shape(64, 64, 56, 56, 3, 3, 1, 1)   # enough pairs per CTA for the dynamic tail
+    x, w, b, _ = O.make_inputs(sh, seed=19, bias=True)
+    xd, wd, bd = (capi.to_dev(t) for t in (x, w, b))
+    p = params_of(sh, has_bias=True)
+    attr = get_device_attributes(0)
+    k = conv2d_gw8_kernel_factory.make_kernel(p, Conv2dGw8Config(wpg=2, tpw=4, pps=2), attr, jit=True)
+    k.compile(attr)
+    k.load(0)
+    live = dead((sh.n, sh.c, sh.p, sh.q), torch.float16)
+    k(live, xd, wd, bd)
+    torch.cuda.synchronize()
+    assert torch.equal(live, capi.fprop(xd, wd, bd, sh, dict(wpg=2, tpw=4, pps=2)))
+    rec = dead((sh.n, sh.c, sh.p, sh.q), torch.float16)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        k(rec, xd, wd, bd)
+    other = dead((sh.n, sh.c, sh.p, sh.q), torch.float16)
+    for _ in range(3):
+        rec.fill_(capi.DEAD_VALUE)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph.replay()
+        k(other, xd, wd, bd)   # live, on the current stream, while the replay runs on its own
+        torch.cuda.synchronize()
+        assert torch.equal(rec, live) and torch.equal(other, live)
+    assert capi.status() == 0
