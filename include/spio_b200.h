@@ -118,10 +118,11 @@ int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, c
  *     just-in-time kernel takes part in the chain like a built-in one.  With dbias the
  *     weight-gradient kernel must be the instantiation that also sums dy
  *     (wgrad_dbias_function).
- *   dp: after the reduce step this rank's dw (and dbias) are stored into every rank's exchange
- *     buffer while the input-gradient kernel runs, and a last small kernel overwrites dw (dbias)
- *     with the sum over the ranks, added in rank order (bit-identical on all ranks).  dw must be
- *     fp32.  `dw_ready`, if given, is then recorded after that sum. */
+ *   dp: after the reduce step one small kernel (spio_dp_allreduce) stores this rank's dw (and
+ *     dbias) into every rank's exchange buffer and overwrites them with the sum over the ranks,
+ *     added in rank order (bit-identical on all ranks), while the input-gradient kernel runs
+ *     beside it.  dw must be fp32.  `dw_ready`, if given, is then recorded after the
+ *     input-gradient kernel, whose completion implies that of the sum. */
 struct spio_dp_exchange;
 typedef struct spio_gw8_backward_opts {
   int dw_f16;
@@ -139,7 +140,7 @@ int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x,
 /* ---- data-parallel sum of the weight gradient ----------------------------------------
  * The path shards by batch (one process per GPU); its only exchange is the sum of the per-rank
  * weight (and bias) gradients, a few thousand floats.  Instead of a host-issued all-reduce the
- * sum runs as two small kernels inside the step's chain of dependent launches: spio_dp_push
+ * sum runs inside the step's chain of dependent launches: spio_dp_push
  * stores the rank's vector [a | b] into slot [rank] of EVERY rank's exchange buffer (plain
  * peer stores over NVLink, then a system-wide fence and a flag), spio_dp_sum waits (bounded:
  * SPIO_STATUS_PEER_TIMEOUT) for all ranks' flags of this exchange and overwrites [a | b] with
@@ -170,6 +171,10 @@ int spio_dp_buffer_close(void* peer_buffer);
 int spio_dp_buffer_free(void* buffer);
 int spio_dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b, void* stream);
 int spio_dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, void* stream);
+/* Both in ONE kernel, which is what the combined backward call launches: its CTAs are small enough
+ * to run on an SM beside a CTA of the convolution kernels, so the exchange overlaps the kernel
+ * that follows it in the stream when that kernel does not wait for it. */
+int spio_dp_allreduce(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, void* stream);
 
 /* Weight gradient for callers that must not allocate device memory.  It has no counterpart
  * in the reference.  Some callers cannot call cudaMalloc at the point where they need the
@@ -203,12 +208,20 @@ int spio_conv2d_gw8_wgrad_host(float* dw, const void* x, const void* dy,
 
 /* One training step of a layer on host buffers: y = fprop(x, w, bias), dx = dgrad(dy, w),
  * dw = wgrad(x, dy) and, if dbias is not NULL (odd number of taps only), dbias.  x and dy are
- * uploaded once, in 32 pieces of the batch; fprop and dgrad of a piece run while the next piece
+ * uploaded once, in 4 to 32 pieces of the batch (16 MB of x or more each); fprop and dgrad of a piece run while the next piece
  * uploads and the previous one's y and dx download, so the call costs about one upload of x and
  * dy instead of the four uploads and two downloads of the three separate calls.  Pinned host
  * memory is needed for the copies to overlap.  Returns after all results are in host memory. */
 int spio_conv2d_gw8_step_host(void* y, void* dx, float* dw, float* dbias, const void* x, const void* dy,
                               const void* w, const float* bias, const spio_gw8_shape* shape);
+/* The same step of a data-parallel rank: after the weight gradient over the rank's images, dw
+ * (and dbias) are summed over the ranks on the device (spio_dp_push / spio_dp_sum, declared
+ * below) before they are copied back, so every rank returns the gradient of the global batch.
+ * dp = NULL is spio_conv2d_gw8_step_host. */
+struct spio_dp_exchange;
+int spio_conv2d_gw8_step_host_dp(void* y, void* dx, float* dw, float* dbias, const void* x, const void* dy,
+                                 const void* w, const float* bias, const spio_gw8_shape* shape,
+                                 const struct spio_dp_exchange* dp);
 
 /* Reports the launch the library would make; kind is SPIO_GW8_FPROP/DGRAD/WGRAD.
  * Needs a CUDA device (it reads the SM count and the shared-memory limit). */
@@ -265,6 +278,17 @@ int spio_conv2d_gw8_wgrad_jit(void* function, float* dw, const void* x, const vo
                               const spio_gw8_shape* shape, const spio_gw8_tune* tune, void* scratch,
                               size_t scratch_bytes, void* stream);
 size_t spio_conv2d_gw8_wgrad_scratch_bytes_jit(const spio_gw8_shape* shape, const spio_gw8_tune* tune);
+
+/* Encodes a tiled TMA tensor map (128 bytes, passed to a kernel by value as a
+ * `const __grid_constant__` parameter) for kernels written against the package's typed headers
+ * (spio_b200/csrc/typed_tma.cuh, generated by spio_b200.generators.TensorMapSpec).  Axes are given
+ * innermost first; strides_bytes has rank - 1 entries (axis 0 is contiguous); swizzle is 0 (none),
+ * 1 (32 B), 2 (64 B) or 3 (128 B).  Needs a CUDA device.  The reference's kernels take plain
+ * pointers (spio/cuda/driver.pyx:182-188); tensor maps are what the typed-dimension layer gains for
+ * sm_100a. */
+int spio_tensor_map_encode(void* map_out, const void* base, int elem_bytes, int rank,
+                           const unsigned long long* sizes, const unsigned long long* strides_bytes,
+                           const unsigned* box, int swizzle);
 
 /* Everything a just-in-time compiled gw8 kernel needs for one launch: the two tensor maps
  * and the geometry it takes by value, the launch dimensions and the status word.  Kernel

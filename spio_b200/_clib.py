@@ -107,6 +107,7 @@ SIGNATURES = {
     "spio_dp_buffer_free": (c_int, [c_void_p]),
     "spio_dp_push": (c_int, [POINTER(DpExchange), c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
     "spio_dp_sum": (c_int, [POINTER(DpExchange), c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
+    "spio_dp_allreduce": (c_int, [POINTER(DpExchange), c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
     "spio_conv2d_gw8_wgrad_static": (
         c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune), c_void_p]),
     "spio_conv2d_gw8_fprop_host": (
@@ -117,6 +118,9 @@ SIGNATURES = {
         c_int, [c_void_p, c_void_p, c_void_p, POINTER(Shape), POINTER(Tune)]),
     "spio_conv2d_gw8_step_host": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape)]),
+    "spio_conv2d_gw8_step_host_dp": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Shape),
+                POINTER(DpExchange)]),
     "spio_conv2d_gw8_plan": (c_int, [c_int, POINTER(Shape), POINTER(Tune), POINTER(PlanInfo)]),
     "spio_conv2d_gw8_plan_for": (
         c_int, [c_int, POINTER(Shape), POINTER(Tune), c_int, c_int, POINTER(PlanInfo)]),
@@ -150,6 +154,9 @@ SIGNATURES = {
         c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
     "spio_b200_device_status": (c_int, [POINTER(c_int)]),
     "spio_b200_status_address": (c_int, [POINTER(c_void_p)]),
+    "spio_tensor_map_encode": (
+        c_int, [c_void_p, c_void_p, c_int, c_int, POINTER(c_ulonglong), POINTER(c_ulonglong),
+                POINTER(ctypes.c_uint), c_int]),
     "spio_b200_last_error": (c_char_p, []),
     "spio_b200_version": (c_char_p, []),
 }

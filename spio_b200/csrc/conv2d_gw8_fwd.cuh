@@ -46,6 +46,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   __shared__ int abort_flag;
   constexpr int DYNQ = 32;         // claims in flight between the load lane and the store lanes
   __shared__ int dynq[DYNQ];       // first unit of every piece the load lane claimed from the pool
+  __shared__ int dynlen[DYNQ];     // and its length in pairs
   __shared__ int dyn_count;        // how many it has claimed so far
   volatile int* const dyn_n = &dyn_count;
 
@@ -151,14 +152,28 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
         };
         load_span(u0, u1);
         if (g.dyn_chunk > 0) {
-          int k = 0;
+          // Pieces shrink as the pool drains (about what is left divided by twice the number of
+          // CTAs, at most g.dyn_chunk pairs), so that the CTAs finish within one small piece of
+          // each other.  A piece of c pairs is streamed in ceil((c + E) / PPS) stages; sizes with
+          // (c + E) a multiple of PPS waste no part of a stage.  What is left is estimated from
+          // the counter value the previous claim returned: a stale value only makes a piece a
+          // little larger than intended, the pieces themselves never overlap.
+          constexpr int CMIN = PPS - (E % PPS);
+          int k = 0, seen = 0;
           while (ok) {
-            const int u = g.dyn_begin + atomicAdd(status + 1 + g.dyn_slot, g.dyn_chunk);
+            int c = (total - g.dyn_begin - seen) / (2 * (int)gridDim.x);
+            if (c > g.dyn_chunk) c = g.dyn_chunk;
+            c = (c + E) / PPS * PPS - E;
+            if (c < CMIN) c = CMIN;
+            const int taken = atomicAdd(status + 1 + g.dyn_slot, c);
+            seen = taken + c;
+            const int u = g.dyn_begin + taken;
             dynq[k & (DYNQ - 1)] = u < total ? u : -1;  // -1: the pool is empty
+            dynlen[k & (DYNQ - 1)] = c;
             __threadfence_block();
             *dyn_n = ++k;
             if (u >= total) break;
-            load_span(u, u + g.dyn_chunk < total ? u + g.dyn_chunk : total);
+            load_span(u, u + c < total ? u + c : total);
           }
         }
         if (ok && mbar_wait(empty(slot), par ^ 1u, abortp)) {
@@ -229,8 +244,9 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
             if (!ok) break;
             __threadfence_block();
             const int u = dynq[k & (DYNQ - 1)];
+            const int c = dynlen[k & (DYNQ - 1)];
             if (u < 0) break;
-            store_span(u, u + g.dyn_chunk < total ? u + g.dyn_chunk : total);
+            store_span(u, u + c < total ? u + c : total);
           }
         }
         tma_store_wait_all();

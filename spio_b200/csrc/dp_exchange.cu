@@ -5,14 +5,15 @@
 // thousand floats -- are added once per step.  An NCCL all-reduce of 18 KB is pure latency, and
 // issuing it from the host needs an event between the reduce and the input-gradient kernel and a
 // stream wait before the next step, both of which break the chain of programmatic dependent
-// launches the step is built from.  Here the exchange is two small kernels inside that chain:
+// launches the step is built from.  Here the exchange is one small kernel inside that chain, right
+// after the weight-gradient reduce and before the input-gradient kernel, which does not wait for it
+// and runs beside it:
 //
-//   push  (after the weight-gradient reduce): each rank stores its vector into slot [rank] of
-//         EVERY rank's exchange buffer (plain st.global to peer memory over NVLink; its own
-//         buffer included), makes the stores visible system-wide and bumps a flag next to the slot;
-//   sum   (after the input-gradient kernel, which overlaps the transfer): each rank waits until
-//         the flags of all ranks show this exchange, adds the slots IN RANK ORDER and overwrites
-//         its vector.  The order is fixed, so all ranks hold bit-identical sums.
+//   push  each rank stores its vector into slot [rank] of EVERY rank's exchange buffer (plain
+//         st.global to peer memory over NVLink; its own buffer included), makes the stores visible
+//         system-wide and bumps a flag next to the slot;
+//   sum   each rank waits until the flags of all ranks show this exchange, adds the slots IN RANK
+//         ORDER and overwrites its vector.  The order is fixed, so all ranks hold bit-identical sums.
 //
 // A remote vector always lands in local memory before it is consumed; there is no remote load, no
 // TMA and no multicast on peer memory.  Slots and flags are double-buffered by the parity of the
@@ -37,7 +38,7 @@ namespace spio_b200 {
 namespace {
 
 constexpr int kMaxWorld = SPIO_DP_MAX_WORLD;
-constexpr size_t kHeaderBytes = 256;  // flags[2][kMaxWorld] u32, then the slots
+constexpr size_t kHeaderBytes = 256;  // flags[2][kMaxWorld] u32, two launch counters, then the slots
 
 struct PeerTable {
   unsigned char* buf[kMaxWorld];
@@ -53,48 +54,71 @@ __device__ __forceinline__ float4* slot_of(unsigned char* buffer, unsigned parit
          ((size_t)parity * world + src_rank) * (capacity / 4);
 }
 
-// Block p copies [a | b] (n_a + n_b floats, both multiples of 4) into slot [rank] of peer p.
-__global__ void __launch_bounds__(256)
-dp_push_kernel(PeerTable peers, const float* __restrict__ a, int n_a, const float* __restrict__ b, int n_b,
-               int rank, int world, unsigned seq, size_t capacity) {
-  grid_dependency_wait();  // the vector is written by the kernel before this one
+// One kernel does both halves of an exchange.  Its CTAs are small on purpose (128 threads, at most
+// 32 registers each, a few bytes of shared memory): they fit on an SM beside a persistent CTA of
+// the convolution kernels, so the exchange runs WHILE the input-gradient kernel that follows it in
+// the stream computes (that kernel does not wait for it), instead of before or after it.
+//
+//   PUSH (CTA p): copy [a | b] (n_a + n_b floats, both multiples of 4) into slot [rank] of rank p,
+//        make the stores visible system-wide, bump the flag next to the slot;
+//   SUM  (CTA p): wait for the flags of all ranks in the local buffer, add slice p of the slots in
+//        rank order, overwrite slice p of [a | b].
+// With both phases in one launch, CTA p's push reads all of [a | b] while other CTAs' sums
+// overwrite slices of it; a CTA therefore starts its sum only after ALL CTAs of the launch have
+// finished their push (a counter in the local buffer's header, re-armed by the last CTA to leave).
+// The sum itself never reads [a | b]: this rank's own copy is in slot [rank] like the others'.
+enum { DP_PUSH = 1, DP_SUM = 2 };
+constexpr int kThreads = 128;
+
+__global__ void __launch_bounds__(kThreads, 16)  // 16 CTAs per SM: at most 32 registers per thread
+dp_exchange_kernel(PeerTable peers, float* __restrict__ a, int n_a, float* __restrict__ b, int n_b, int rank,
+                   int world, unsigned seq, size_t capacity, int phases, int* __restrict__ status) {
+  __shared__ int ok;
+  // the kernel after this one (the input-gradient kernel) may start at once; this one needs the
+  // vector, which the kernel before it writes
   grid_dependency_launch_dependents();
+  grid_dependency_wait();
   const int p = blockIdx.x;
   const unsigned parity = seq & 1u;
-  float4* dst = slot_of(peers.buf[p], parity, world, rank, capacity);
-  const float4* a4 = reinterpret_cast<const float4*>(a);
-  const float4* b4 = reinterpret_cast<const float4*>(b);
-  const int na4 = n_a / 4, nb4 = n_b / 4;
-  for (int i = threadIdx.x; i < na4 + nb4; i += blockDim.x) dst[i] = i < na4 ? a4[i] : b4[i - na4];
-  __threadfence_system();  // every thread's stores are visible to the peer before the flag is
-  __syncthreads();
-  if (threadIdx.x == 0) atomicAdd_system(flag_of(peers.buf[p], parity, rank), 1u);
-}
-
-// dst = sum over ranks, in rank order, of the slots of exchange `seq` in this rank's buffer.
-__global__ void __launch_bounds__(256)
-dp_sum_kernel(unsigned char* local, float* __restrict__ a, int n_a, float* __restrict__ b, int n_b, int world,
-              unsigned seq, size_t capacity, int* __restrict__ status) {
-  __shared__ int ok;
-  grid_dependency_launch_dependents();
-  grid_dependency_wait();  // the vector must not be overwritten before the push has read it
-  const unsigned parity = seq & 1u;
+  const int na4 = n_a / 4, nb4 = n_b / 4, n4 = na4 + nb4;
+  unsigned char* local = peers.buf[rank];
+  unsigned* done = reinterpret_cast<unsigned*>(local) + 2 * kMaxWorld;  // CTAs of this launch that have pushed
+  if (phases & DP_PUSH) {
+    float4* dst = slot_of(peers.buf[p], parity, world, rank, capacity);
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    const float4* b4 = reinterpret_cast<const float4*>(b);
+    for (int i = threadIdx.x; i < n4; i += kThreads) dst[i] = i < na4 ? a4[i] : b4[i - na4];
+    __threadfence_system();  // every thread's stores are visible to the peer before the flag is
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      atomicAdd_system(flag_of(peers.buf[p], parity, rank), 1u);
+      if (phases & DP_SUM) atomicAdd(done, 1u);
+    }
+  }
+  if (!(phases & DP_SUM)) return;
   const unsigned expect = (seq >> 1) + 1u;  // flags count the exchanges of this parity so far
   if (threadIdx.x == 0) {
     int good = 1;
     u64 t0 = 0;
+    auto waiting = [&](u32 it) {  // false once the limit has passed
+      if ((it & 63u) != 0u) return true;
+      const u64 now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      return now - t0 <= SPIO_WAIT_LIMIT_NS;
+    };
     for (int r = 0; r < world && good; ++r) {
       volatile unsigned* f = flag_of(local, parity, r);
-      for (u32 it = 1; (int)(*f - expect) < 0; ++it) {
-        if ((it & 63u) == 0u) {
-          const u64 now = globaltimer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > SPIO_WAIT_LIMIT_NS) {
-            good = 0;
-            break;
-          }
+      for (u32 it = 1; (int)(*f - expect) < 0; ++it)
+        if (!waiting(it)) {
+          good = 0;
+          break;
         }
-      }
+    }
+    // [a | b] may be overwritten only after every CTA of this launch has read it for its push
+    if (phases & DP_PUSH) {
+      volatile unsigned* d = done;
+      for (u32 it = 1; good && *d < (unsigned)gridDim.x; ++it)
+        if (!waiting(it)) good = 0;
     }
     __threadfence_system();  // the slots are read only after the flags were seen
     ok = good;
@@ -104,27 +128,38 @@ dp_sum_kernel(unsigned char* local, float* __restrict__ a, int n_a, float* __res
     if (threadIdx.x == 0) atomicExch(status, (int)GW8_PEER_TIMEOUT);
     return;
   }
-  const int na4 = n_a / 4, nb4 = n_b / 4;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= na4 + nb4) return;
-  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int r = 0; r < world; ++r) {
-    const float4 v = __ldcg(slot_of(local, parity, world, r, capacity) + i);  // L2: written by peers
-    sum.x += v.x;
-    sum.y += v.y;
-    sum.z += v.z;
-    sum.w += v.w;
+  const int i0 = (int)((long long)n4 * p / gridDim.x), i1 = (int)((long long)n4 * (p + 1) / gridDim.x);
+  for (int i = i0 + threadIdx.x; i < i1; i += kThreads) {
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = __ldcg(slot_of(local, parity, world, r, capacity) + i);  // L2: written by peers
+      sum.x += v.x;
+      sum.y += v.y;
+      sum.z += v.z;
+      sum.w += v.w;
+    }
+    if (i < na4)
+      reinterpret_cast<float4*>(a)[i] = sum;
+    else
+      reinterpret_cast<float4*>(b)[i - na4] = sum;
   }
-  if (i < na4)
-    reinterpret_cast<float4*>(a)[i] = sum;
-  else
-    reinterpret_cast<float4*>(b)[i - na4] = sum;
+  // the last CTA to finish re-arms the counter for the next launch
+  if (phases & DP_PUSH) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned* left = done + 1;
+      if (atomicAdd(left, 1u) == gridDim.x - 1) {
+        *done = 0;
+        *left = 0;
+      }
+    }
+  }
 }
 
 int launch(const void* func, int grid, void** args, cudaStream_t stream) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(256);
+  cfg.blockDim = dim3(kThreads);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -153,29 +188,32 @@ int check(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b
 
 }  // namespace
 
-int dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b,
-            cudaStream_t stream) {
+int dp_exchange(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, int phases,
+                cudaStream_t stream) {
   if (check(dp, a, n_a, b, n_b)) return 1;
+  int* status = nullptr;
+  if (gw8_status_pointer(&status)) return 1;
   PeerTable peers{};
   for (int r = 0; r < dp->world; ++r) peers.buf[r] = static_cast<unsigned char*>(dp->buffers[r]);
   int na = (int)n_a, nb = (int)n_b, rank = dp->rank, world = dp->world;
   unsigned seq = dp->seq;
   size_t capacity = dp->capacity;
-  void* args[] = {&peers, &a, &na, &b, &nb, &rank, &world, &seq, &capacity};
-  return launch(reinterpret_cast<const void*>(&dp_push_kernel), world, args, stream);
+  void* args[] = {&peers, &a, &na, &b, &nb, &rank, &world, &seq, &capacity, &phases, &status};
+  // one CTA per rank: CTA p pushes to rank p and sums slice p
+  return launch(reinterpret_cast<const void*>(&dp_exchange_kernel), world, args, stream);
+}
+
+int dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b,
+            cudaStream_t stream) {
+  return dp_exchange(dp, const_cast<float*>(a), n_a, const_cast<float*>(b), n_b, DP_PUSH, stream);
 }
 
 int dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, cudaStream_t stream) {
-  if (check(dp, a, n_a, b, n_b)) return 1;
-  int* status = nullptr;
-  if (gw8_status_pointer(&status)) return 1;
-  unsigned char* local = static_cast<unsigned char*>(dp->buffers[dp->rank]);
-  int na = (int)n_a, nb = (int)n_b, world = dp->world;
-  unsigned seq = dp->seq;
-  size_t capacity = dp->capacity;
-  void* args[] = {&local, &a, &na, &b, &nb, &world, &seq, &capacity, &status};
-  const int grid = (int)((n_a + n_b) / 4 + 255) / 256;
-  return launch(reinterpret_cast<const void*>(&dp_sum_kernel), grid, args, stream);
+  return dp_exchange(dp, a, n_a, b, n_b, DP_SUM, stream);
+}
+
+int dp_allreduce(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, cudaStream_t stream) {
+  return dp_exchange(dp, a, n_a, b, n_b, DP_PUSH | DP_SUM, stream);
 }
 
 }  // namespace spio_b200
@@ -239,6 +277,10 @@ int spio_dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const f
 
 int spio_dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, void* stream) {
   return dp_sum(dp, a, n_a, b, n_b, (cudaStream_t)stream);
+}
+
+int spio_dp_allreduce(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, void* stream) {
+  return dp_allreduce(dp, a, n_a, b, n_b, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -321,13 +321,43 @@ bool pair_images_enabled() {
   return on;
 }
 
-// Pairs per claim of the forward kernel's dynamic tail; SPIO_DYN=<n> changes it, SPIO_DYN=0
-// turns the dynamic tail off.
+// SPIO_CHUNK_INNER=0 / 1: order of the forward kernel's work when there are several 64-channel
+// chunks (see Gw8Geom::chunk_inner).
+bool chunk_inner_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("SPIO_CHUNK_INNER");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+
+// Largest piece (in pairs) a CTA claims from the pool of the forward kernel's dynamic tail (pieces
+// shrink as the pool drains); SPIO_DYN=<n> changes it, SPIO_DYN=0 turns the dynamic tail off.
 int dyn_chunk_setting() {
   static const int v = [] {
     const char* e = getenv("SPIO_DYN");
-    const int n = e ? atoi(e) : 4;
+    const int n = e ? atoi(e) : 7;
     return n > 0 && n <= 64 ? n : 0;
+  }();
+  return v;
+}
+
+// Pairs per CTA from which the dynamic tail is used.
+int dyn_min_pairs() {
+  static const int v = [] {
+    const char* e = getenv("SPIO_DYN_MIN_PAIRS");
+    const int n = e ? atoi(e) : 72;
+    return n >= 4 ? n : 72;
+  }();
+  return v;
+}
+
+// Largest share of the work (per cent) the dynamic pool may take; SPIO_DYN_POOL changes it.
+int dyn_pool_percent() {
+  static const int v = [] {
+    const char* e = getenv("SPIO_DYN_POOL");
+    const int n = e ? atoi(e) : 25;
+    return n >= 1 && n <= 100 ? n : 25;
   }();
   return v;
 }
@@ -508,12 +538,18 @@ int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int
   } else {
     pl.threads = v->fwd_threads;
     pl.grid = (int)(total < ctas ? total : ctas);
-    // Dynamic tail: the last 8 pairs per CTA on average are not assigned statically but claimed
-    // from a pool, when a CTA has enough work for it.
+    g.chunk_inner = (g.n_chunks > 1 && chunk_inner_enabled()) ? 1 : 0;
+    // Dynamic tail: the last quarter of the work (at most 2 * chunk pairs per CTA on average) is not
+    // assigned statically but claimed from a pool, when a CTA has enough work for it.  Every piece
+    // re-reads a halo and every claim is a round trip to a global counter, which costs more than the
+    // better balance gains while a CTA has few pairs: measured on the 64-channel 56 x 56 layer,
+    // 97 pairs per CTA (512 images) 73.8 -> 70.6 us with the pool, 48 pairs (256 images) 39.1 -> 40.1 us,
+    // 24 pairs (128 images) 22.3 -> 25.9 us.  SPIO_DYN_MIN_PAIRS moves the threshold.
     const int chunk = dyn_chunk_setting();
-    if (chunk > 0 && total >= 16LL * pl.grid * chunk / 4) {
+    if (chunk > 0 && total >= (long long)dyn_min_pairs() * pl.grid) {
       long long pool = 2LL * chunk * pl.grid;
-      if (pool > total / 4) pool = total / 4;
+      const long long cap = total * dyn_pool_percent() / 100;
+      if (pool > cap) pool = cap;
       g.dyn_chunk = chunk;
       g.dyn_begin = (int)(total - pool);
     }
@@ -901,10 +937,12 @@ int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x,
                                     both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE,
                                     both ? L2_HINT_EVICT_LAST : L2_HINT_NONE, dbias, wgrad_fn, o.dw_f16))
     return 1;
-  // Data-parallel: this rank's dw (and dbias) go to every rank's exchange buffer while the
-  // input-gradient kernel runs; the sum over the ranks follows that kernel.  No event, no second
-  // stream: the chain of dependent launches stays intact.
-  if (o.dp != nullptr && dp_push(o.dp, static_cast<const float*>(dw), dw_floats, dbias, db_floats, st)) return 1;
+  // Data-parallel: one small kernel stores this rank's dw (and dbias) into every rank's exchange
+  // buffer, waits for the others' and overwrites dw with the sum in rank order.  Its CTAs fit on
+  // an SM beside a CTA of the input-gradient kernel, which does not wait for it, so the exchange
+  // runs while that kernel computes.  No event, no second stream: the chain of dependent
+  // launches stays intact.
+  if (o.dp != nullptr && dp_allreduce(o.dp, static_cast<float*>(dw), dw_floats, dbias, db_floats, st)) return 1;
   if (dw != nullptr && dw_ready != nullptr && o.dp == nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
   // dgrad reads dy and w and writes dx; the weight-gradient kernels read x and dy and write
   // scratch and dw (the exchange reads dw and writes the exchange buffers).  Neither touches what
@@ -912,10 +950,9 @@ int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x,
   if (dx != nullptr && launch_fwd(SPIO_GW8_DGRAD, dx, dy, w, nullptr, shape, dgrad_tune, st, dw != nullptr,
                                   both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE, o.dgrad_function))
     return 1;
-  if (o.dp != nullptr) {
-    if (dp_sum(o.dp, static_cast<float*>(dw), dw_floats, dbias, db_floats, st)) return 1;
-    if (dw_ready != nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
-  }
+  // the input-gradient kernel completes only after everything before it (it waits at its end), so
+  // an event recorded here also covers the sum over the ranks
+  if (o.dp != nullptr && dw_ready != nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
   return 0;
 }
 
@@ -1013,6 +1050,12 @@ int spio_conv2d_gw8_fprop_host(void* y, const void* x, const void* w, const floa
 
 int spio_conv2d_gw8_step_host(void* y, void* dx, float* dw, float* dbias, const void* x, const void* dy,
                               const void* w, const float* bias, const spio_gw8_shape* shape) {
+  return spio_conv2d_gw8_step_host_dp(y, dx, dw, dbias, x, dy, w, bias, shape, nullptr);
+}
+
+int spio_conv2d_gw8_step_host_dp(void* y, void* dx, float* dw, float* dbias, const void* x, const void* dy,
+                                 const void* w, const float* bias, const spio_gw8_shape* shape,
+                                 const spio_dp_exchange* dp) {
   if (check_shape(shape)) return 1;
   if (y == nullptr || dx == nullptr || dw == nullptr || x == nullptr || dy == nullptr || w == nullptr)
     return fail("NULL host pointer");
@@ -1044,8 +1087,13 @@ int spio_conv2d_gw8_step_host(void* y, void* dx, float* dw, float* dbias, const 
   const float* d_bias = bias ? static_cast<const float*>(st->buf[3]) : nullptr;
   GW8_CUDA(cudaMemcpyAsync(st->buf[2], w, wb, cudaMemcpyHostToDevice, st->up));
   if (bias) GW8_CUDA(cudaMemcpyAsync(st->buf[3], bias, bb, cudaMemcpyHostToDevice, st->up));
+  // Pieces of at least 16 MB of x (a copy much smaller than that does not reach the link rate),
+  // at least 4 so that uploads, kernels and downloads overlap, at most kStepChunks.
   const int n = shape->n;
-  const int pieces = n < kStepChunks ? n : kStepChunks;
+  int pieces = (int)(xb >> 24);
+  if (pieces < 4) pieces = 4;
+  if (pieces > kStepChunks) pieces = kStepChunks;
+  if (pieces > n) pieces = n;
   const size_t x_img = xb / (size_t)n, y_img = yb / (size_t)n;
   // Piece i: upload its images of x and dy; as soon as they are there, fprop and dgrad run on
   // them; as soon as those are done, y and dx of the piece go back.  The three streams overlap,
@@ -1071,6 +1119,13 @@ int spio_conv2d_gw8_step_host(void* y, void* dx, float* dw, float* dbias, const 
   if (launch_wgrad(static_cast<float*>(st->buf[7]), d_x, d_dy, shape, nullptr, st->buf[4], scratch, st->stream,
                    L2_HINT_NONE, L2_HINT_NONE, dbias ? static_cast<float*>(st->buf[8]) : nullptr))
     return 1;
+  // data-parallel: the sum over the ranks happens on the device, before dw goes back
+  if (dp != nullptr) {
+    float* d_dw = static_cast<float*>(st->buf[7]);
+    float* d_db = dbias ? static_cast<float*>(st->buf[8]) : nullptr;
+    const size_t n_dw = weight_elems(shape), n_db = dbias ? (size_t)shape->c : 0;
+    if (dp_allreduce(dp, d_dw, n_dw, d_db, n_db, st->stream)) return 1;
+  }
   GW8_CUDA(cudaEventRecord(st->computed[kStepChunks], st->stream));
   GW8_CUDA(cudaStreamWaitEvent(st->down, st->computed[kStepChunks], 0));
   GW8_CUDA(cudaMemcpyAsync(dw, st->buf[7], dwb, cudaMemcpyDeviceToHost, st->down));
@@ -1186,6 +1241,52 @@ int spio_conv2d_gw8_wgrad_reduce(float* dw, float* dbias, const float* scratch, 
   if (dw == nullptr || scratch == nullptr || c <= 0 || c % 8 || taps <= 0 || n_parts <= 0)
     return fail("bad argument");
   return launch_reduce(dw, dbias, scratch, c, taps, n_parts, (cudaStream_t)stream);
+}
+
+int spio_tensor_map_encode(void* map_out, const void* base, int elem_bytes, int rank,
+                           const unsigned long long* sizes, const unsigned long long* strides_bytes,
+                           const unsigned* box, int swizzle) {
+  if (map_out == nullptr || base == nullptr || sizes == nullptr || box == nullptr) return fail("NULL argument");
+  if (rank < 1 || rank > 5) return fail("a tiled tensor map has 1 to 5 axes");
+  if (rank > 1 && strides_bytes == nullptr) return fail("strides_bytes is NULL");
+  CUtensorMapDataType type;
+  switch (elem_bytes) {
+    case 1: type = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case 2: type = CU_TENSOR_MAP_DATA_TYPE_UINT16; break;
+    case 4: type = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;
+    case 8: type = CU_TENSOR_MAP_DATA_TYPE_UINT64; break;
+    default: return fail("element size must be 1, 2, 4 or 8 bytes");
+  }
+  static const CUtensorMapSwizzle kSwizzle[4] = {CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
+                                                 CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_SWIZZLE_128B};
+  if (swizzle < 0 || swizzle > 3) return fail("swizzle must be 0 (none), 1 (32 B), 2 (64 B) or 3 (128 B)");
+  if ((reinterpret_cast<size_t>(base) & 15u) != 0) return fail("tensor pointers must be 16-byte aligned");
+  if (((size_t)box[0] * elem_bytes) % 16 != 0) return fail("the innermost box extent must be a multiple of 16 bytes");
+  const DeviceInfo* d = nullptr;
+  if (device_info(&d)) return 1;  // loads the driver entry point
+  cuuint64_t dims[5], strides[4];
+  cuuint32_t bx[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    if (sizes[i] == 0 || box[i] == 0 || box[i] > 256) return fail("sizes must be positive and box extents 1..256");
+    dims[i] = sizes[i];
+    bx[i] = box[i];
+    estr[i] = 1;
+    if (i > 0) {
+      if (strides_bytes[i - 1] % 16 != 0) return fail("tensor strides must be multiples of 16 bytes");
+      strides[i - 1] = strides_bytes[i - 1];
+    }
+  }
+  CUtensorMap m;
+  const CUresult r = g_encode(&m, type, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, bx, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, kSwizzle[swizzle], CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[96];
+    snprintf(buf, sizeof buf, "CUDA error: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return fail(buf);
+  }
+  memcpy(map_out, &m, sizeof m);
+  return 0;
 }
 
 int spio_b200_status_address(void** address) {

@@ -66,6 +66,11 @@ struct Gw8Geom {
   int dyn_slot;        // which pair of counters behind the status word this launch uses
   int hint_in;         // L2 eviction hint (L2_HINT_*) for loads of the streamed operand
   int hint_tiled;      // wgrad: the same for loads of dy
+  int chunk_inner;     // fprop/dgrad: order of the flattened work.  0: chunk, image group, column
+                       // tile, pair (a CTA stays in one 64-channel chunk); 1: image group, column
+                       // tile, chunk, pair (a CTA does all chunks of an image one after the other,
+                       // so the 128-byte pieces of a pixel's channels are read and written within a
+                       // short time of each other)
   int pair_images;     // fprop/dgrad, images at most 8 pixels wide: the two 8-pixel halves of a
                        // 16-pixel block tile are pixels 0-7 of two consecutive images of the slot
                        // (wt = 8, nb even, ntiles = nb / 2)
@@ -136,19 +141,27 @@ struct Gw8Segment {
 // sequence and cuts it into segments.  Every role of a CTA (load, compute, store)
 // runs the same walk, so they agree on the order of slots without communicating.
 struct Gw8Walk {
-  int u, u1, n_pairs, n_ct, n_ig;
+  int u, u1, n_pairs, n_ct, n_ig, n_chunks_inner;
 
   __device__ __forceinline__ Gw8Walk(int u0_, int u1_, const Gw8Geom& g)
-      : u(u0_), u1(u1_), n_pairs(g.n_pairs), n_ct(g.n_ct), n_ig(g.n_ig) {}
+      : u(u0_), u1(u1_), n_pairs(g.n_pairs), n_ct(g.n_ct), n_ig(g.n_ig),
+        n_chunks_inner(g.chunk_inner ? g.n_chunks : 0) {}
 
   __device__ __forceinline__ bool next(Gw8Segment& s) {
     if (u >= u1) return false;
     int m = u % n_pairs;
     int rest = u / n_pairs;
-    s.ct = rest % n_ct;
-    rest /= n_ct;
-    s.ig = rest % n_ig;
-    s.ck = rest / n_ig;
+    if (n_chunks_inner > 0) {
+      s.ck = rest % n_chunks_inner;
+      rest /= n_chunks_inner;
+      s.ct = rest % n_ct;
+      s.ig = rest / n_ct;
+    } else {
+      s.ct = rest % n_ct;
+      rest /= n_ct;
+      s.ig = rest % n_ig;
+      s.ck = rest / n_ig;
+    }
     s.m0 = m;
     int len = n_pairs - m;
     if (len > u1 - u) len = u1 - u;

@@ -51,6 +51,7 @@ int gw8_status_pointer(int** status);  // device address of the current device's
 int dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b,
             cudaStream_t stream);
 int dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, cudaStream_t stream);
+int dp_allreduce(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, cudaStream_t stream);
 
 // Driver-API launch of a just-in-time compiled function (jit_driver.cpp).
 int jit_launch(void* function, int grid, int block, int smem_bytes, cudaStream_t stream, void** args,

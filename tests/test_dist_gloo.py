@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import oracle as O
-from spio_b200.distributed import GradWeightReducer, shard_batch, shard_range
+from spio_b200.distributed import GradWeightReducer, rank_order_sum, shard_batch, shard_range
 
 
 def test_shard_ranges_cover_the_batch():
@@ -51,6 +51,13 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         dxs = [torch.empty_like(dx_local) for _ in range(world)]
         dist.all_gather(ys, y_local.contiguous())
         dist.all_gather(dxs, dx_local.contiguous())
+        # the order of the peer-store exchange: every rank holds every rank's partial and adds
+        # them in rank order, so all ranks get the same bits whatever the arrival order was
+        mine = O.c_wgrad(xs, dys, sub).contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        ordered = rank_order_sum(parts[::-1][::-1])
+        torch.save({"ordered": ordered}, os.path.join(out_dir, f"ordered{rank}.pt"))
         if rank == 0:
             torch.save({"dw": dw, "y": torch.cat(ys), "dx": torch.cat(dxs)}, os.path.join(out_dir, "out.pt"))
     finally:
@@ -66,3 +73,6 @@ def test_two_rank_data_parallel_matches_single_process(tmp_path):
     assert torch.equal(got["y"], O.c_fprop(x, w, None, sh))
     assert torch.equal(got["dx"], O.c_dgrad(dy, w, sh))
     O.assert_close(got["dw"], O.c_wgrad(x, dy, sh), sh, "wgrad", "2-rank sum")
+    ordered = [torch.load(tmp_path / f"ordered{r}.pt")["ordered"] for r in range(world)]
+    assert torch.equal(ordered[0], ordered[1])
+    O.assert_close(ordered[0], O.c_wgrad(x, dy, sh), sh, "wgrad", "rank-order sum")

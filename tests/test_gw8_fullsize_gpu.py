@@ -114,9 +114,10 @@ def test_host_buffer_entry_points_match_device_entry_points():
 
 def test_dynamic_tail_gives_identical_results():
     """The forward kernel's load warps claim the tail of the work from a global pool, in pieces
-    of SPIO_DYN pairs (default 4, 0 = off).  The setting is read once per process, so the
-    comparison runs in child processes: fprop and dgrad must be bit-identical with and without it, on a shape
-    large enough for the pool to be used and over repeated launches (the counters are reused)."""
+    of at most SPIO_DYN pairs that shrink as the pool drains (default 7, 0 = off; used from
+    SPIO_DYN_MIN_PAIRS pairs per CTA).  The settings are read once per process, so the comparison
+    runs in child processes: fprop and dgrad must be bit-identical with and without it, with the
+    pool in use and over repeated launches (the counters are reused)."""
     import os
     import subprocess
     import sys
@@ -138,9 +139,9 @@ def test_dynamic_tail_gives_identical_results():
     """)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     results = []
-    for setting in ("0", "4", "7"):
+    for setting in ("0", "2", "7", "12"):
         path = os.path.join(root, "tests", f"_dyn_{setting}.pt")
-        env = dict(os.environ, SPIO_DYN=setting, PYTHONPATH=root)
+        env = dict(os.environ, SPIO_DYN=setting, SPIO_DYN_MIN_PAIRS="8", PYTHONPATH=root)
         subprocess.run([sys.executable, "-c", code, path], check=True, env=env, cwd=root, timeout=300)
         results.append(torch.load(path))
         os.remove(path)
