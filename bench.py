@@ -385,6 +385,9 @@ def run_ours(args) -> None:
             px.close()
             px = None
             collective = "nccl all-reduce on a side stream, overlapped with dgrad (peer exchange failed on a rank)"
+    if world == 1 and args.force_exchange:   # one rank exchanging with itself: the cost of the chain alone
+        px = PeerExchange(C * 8 * R * S + C, device=dev)
+        collective = "peer-store exchange with itself (1 GPU, --force-exchange)"
     comm = torch.cuda.Stream(dev) if world > 1 and px is None else None
 
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -790,6 +793,8 @@ def main() -> None:
     ap.add_argument("--no-sustained", action="store_true", help="skip the 200-step run")
     ap.add_argument("--collective", choices=["peer", "nccl"], default="peer",
                     help="how dw is summed over the ranks (N > 1)")
+    ap.add_argument("--force-exchange", action="store_true",
+                    help="1 GPU: run the peer-store exchange with the rank itself")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="images over all ranks (default: the 2048 of the data-parallel sweep)")
     ap.add_argument("--tune", default="",

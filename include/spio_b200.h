@@ -140,15 +140,18 @@ int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x,
 /* ---- data-parallel sum of the weight gradient ----------------------------------------
  * The path shards by batch (one process per GPU); its only exchange is the sum of the per-rank
  * weight (and bias) gradients, a few thousand floats.  Instead of a host-issued all-reduce the
- * sum runs inside the step's chain of dependent launches: spio_dp_push
- * stores the rank's vector [a | b] into slot [rank] of EVERY rank's exchange buffer (plain
- * peer stores over NVLink, then a system-wide fence and a flag), spio_dp_sum waits (bounded:
- * SPIO_STATUS_PEER_TIMEOUT) for all ranks' flags of this exchange and overwrites [a | b] with
- * the slots added in rank order.  Remote data always lands in local memory before it is used;
- * nothing loads from a peer, and no TMA or multicast touches peer memory.  The reference has no
+ * sum runs inside the step's chain of dependent launches: every thread of spio_dp_allreduce owns
+ * four floats of the vector [a | b]; it stores them, each paired with a tag that names the
+ * exchange, into slot [rank] of EVERY rank's exchange buffer (plain 16-byte peer stores over
+ * NVLink), then polls the same four floats of all ranks' slots in its own buffer until the tags
+ * match (bounded: SPIO_STATUS_PEER_TIMEOUT), adds them in rank order and overwrites its floats.
+ * Data and tag travel in one 8-byte word, so there are no flags, fences or atomics, and all ranks
+ * get bit-identical sums.  Remote data always lands in local memory before it is used; nothing
+ * loads from a peer, and no TMA or multicast touches peer memory.  The reference has no
  * multi-device support (its kernel cache is merely keyed by device ordinal,
  * spio/kernels/kernel_key.py:13-18); a trainer would otherwise call torch.distributed.all_reduce
- * on grad_weight after spio/functional/conv2d_gw8_function.py:147.
+ * on grad_weight after spio/functional/conv2d_gw8_function.py:147.  spio_dp_push and spio_dp_sum
+ * are the two halves as separate launches (for tests that emulate several ranks on one GPU).
  *
  * Set-up, once: every rank allocates a buffer of spio_dp_buffer_bytes(world, capacity) with
  * spio_dp_buffer_alloc (zero-filled; returns a 64-byte CUDA IPC handle), the ranks exchange the
@@ -171,9 +174,7 @@ int spio_dp_buffer_close(void* peer_buffer);
 int spio_dp_buffer_free(void* buffer);
 int spio_dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b, void* stream);
 int spio_dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, void* stream);
-/* Both in ONE kernel, which is what the combined backward call launches: its CTAs are small enough
- * to run on an SM beside a CTA of the convolution kernels, so the exchange overlaps the kernel
- * that follows it in the stream when that kernel does not wait for it. */
+/* Both halves in ONE kernel, which is what the combined backward call launches. */
 int spio_dp_allreduce(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, void* stream);
 
 /* Weight gradient for callers that must not allocate device memory.  It has no counterpart

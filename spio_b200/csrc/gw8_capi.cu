@@ -938,10 +938,8 @@ int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x,
                                     both ? L2_HINT_EVICT_LAST : L2_HINT_NONE, dbias, wgrad_fn, o.dw_f16))
     return 1;
   // Data-parallel: one small kernel stores this rank's dw (and dbias) into every rank's exchange
-  // buffer, waits for the others' and overwrites dw with the sum in rank order.  Its CTAs fit on
-  // an SM beside a CTA of the input-gradient kernel, which does not wait for it, so the exchange
-  // runs while that kernel computes.  No event, no second stream: the chain of dependent
-  // launches stays intact.
+  // buffer, waits for the others' and overwrites dw with the sum in rank order (2-3 us).  No event,
+  // no second stream: the chain of dependent launches stays intact.
   if (o.dp != nullptr && dp_allreduce(o.dp, static_cast<float*>(dw), dw_floats, dbias, db_floats, st)) return 1;
   if (dw != nullptr && dw_ready != nullptr && o.dp == nullptr) GW8_CUDA(cudaEventRecord((cudaEvent_t)dw_ready, st));
   // dgrad reads dy and w and writes dx; the weight-gradient kernels read x and dy and write

@@ -17,8 +17,10 @@
 // (its loaders are cp.async based: spio/include/spio/async_loader.cuh, memory.cuh:17-24).
 #pragma once
 
-#include "typed.h"
+#include <cuda_fp16.h>
+
 #include "gw8_common.cuh"
+#include "typed.h"
 
 namespace spio_b200 {
 namespace typed {

@@ -9,6 +9,7 @@ raise.
 
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -23,6 +24,10 @@ from ..util.tensor_format import to_channels_last
 # kernel rounds its fp32 sums once and stores the weight's own type, which saves the cast kernel
 # autograd launches to hand an fp16 parameter (or autocast's fp16 copy of it) its gradient.
 _grad_weight_dtype = torch.float32
+
+# SPIO_CHECK_STATUS=1: every backward pass synchronises and checks the kernels' status word
+# (spio_b200.check_status); off by default because of the synchronisation.
+_CHECK_STATUS = os.environ.get("SPIO_CHECK_STATUS", "0") == "1"
 
 
 def set_grad_weight_dtype(dtype: torch.dtype) -> None:
@@ -140,6 +145,10 @@ def conv2d_gw8_backward_op(
                         grad_bias if fused_bias else None)
     elif needs_input_grad:
         dgrad_kernel(grad_input, grad_output, weight, None)
+    if _CHECK_STATUS:
+        from .. import check_status
+
+        check_status()
     return grad_input, grad_weight, grad_bias
 
 

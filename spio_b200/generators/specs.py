@@ -9,6 +9,7 @@ declared before it is used and declares dimensions that are only mentioned by na
 from __future__ import annotations
 
 import re
+import textwrap
 from enum import Enum
 from typing import Dict, Iterable, Iterator, List, Optional, Sequence, Tuple, Union
 
@@ -420,7 +421,10 @@ def generate(specs: Iterable[GenSpec], namespace: Optional[str] = None, tma: Opt
     ordered = _ordered(list(specs))
     if tma is None:
         tma = any(isinstance(s, (TensorMapSpec, MbarrierRing, TileConfig)) for s in ordered)
-    lines = ["#pragma once", '#include "typed_tma.cuh"' if tma else '#include "typed.h"']
+    lines = ["#pragma once"]
+    if any(getattr(s, "data_type", None) in (dtype.half, dtype.half2) for s in ordered):
+        lines.append("#include <cuda_fp16.h>")
+    lines.append('#include "typed_tma.cuh"' if tma else '#include "typed.h"')
     if any(isinstance(s, TileConfig) for s in ordered):
         lines.append('#include "gw8_common.cuh"')
     lines.append("")
@@ -432,7 +436,7 @@ def generate(specs: Iterable[GenSpec], namespace: Optional[str] = None, tma: Opt
     return "\n".join(lines) + "\n"
 
 
-SPIO_BLOCK = re.compile(r"/\*@spio\s*(.*?)\s*@spio\*/", re.DOTALL)
+SPIO_BLOCK = re.compile(r"/\*@spio[ \t]*\n?(.*?)@spio\*/", re.DOTALL)
 
 
 def extract_specs(source: str) -> Generators:
@@ -444,13 +448,18 @@ def extract_specs(source: str) -> Generators:
     scope = {"__builtins__": {}, "dtype": dtype, "Dims": Dims, "Strides": Strides, "Dim": Dim, "Fold": Fold,
              "Tensor": Tensor, "CompoundIndex": CompoundIndex, "TensorMapSpec": TensorMapSpec,
              "MbarrierRing": MbarrierRing, "TileConfig": TileConfig}
-    for block in SPIO_BLOCK.findall(source):
-        local: Dict[str, object] = {}
-        exec(block, dict(scope, **{k: v for k, v in g.items()}), local)  # noqa: S102 - restricted scope
-        for name, value in local.items():
+    class Naming(dict):
+        """Block-level names: a specification is named the moment it is assigned, so that later
+        lines of the same block can use it (``I = Dim()`` then ``Dims(I(16))``)."""
+
+        def __setitem__(self, name, value):
             if isinstance(value, GenSpec):
                 setattr(g, name, value)
-                scope[name] = value
+            super().__setitem__(name, value)
+
+    names = Naming()
+    for block in SPIO_BLOCK.findall(source):
+        exec(textwrap.dedent(block), scope, names)  # noqa: S102 - no builtins, generator classes only
     return g
 
 

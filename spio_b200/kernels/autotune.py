@@ -3,13 +3,15 @@
 The reference collects (kernel, params, config, latency) rows by running a model under
 torch.profiler with random configuration overlays and trains one XGBoost regressor per kernel
 from them (scripts/profile_block.py:551-701, scripts/train_performance_model.py:46-142).  Here
-each configuration of a kernel family's configuration space is timed directly with CUDA events
-on operands larger than the L2 cache; the fastest goes into the tuning table that
+each configuration of a kernel family's configuration space is timed directly with CUDA events,
+in chains of back-to-back launches that rotate over operand sets larger than the L2 cache (the
+way the kernels run in a training step); the fastest goes into the tuning table that
 ``PerformanceModelCache`` consults first, and all rows can be fitted by the small
 gradient-boosted-tree model in ``gbt_model.py`` for shapes that were never measured.
 
-    python -m spio_b200.kernels.autotune --shape 256,64,56,56 --shape 256,128,56,56 \
-        --out spio_b200/kernels/perf_models --rows _rows.csv --fit
+    python -m spio_b200.kernels.autotune --shape 256,64,56,56 --shapes-file tests/golden/model_shapes.json \
+        --out spio_b200/kernels/perf_models --rows rows.csv          # on the GPU
+    python -m spio_b200.kernels.autotune --from-rows rows.csv --out spio_b200/kernels/perf_models   # anywhere
 """
 
 from __future__ import annotations
@@ -37,41 +39,55 @@ KERNELS = {
 }
 
 
-def make_args(kernel_name: str, params: Conv2dGw8Params, device) -> tuple:
-    """Operands in the order the kernel takes them (random contents, channels_last)."""
+def make_operand_sets(kernel_name: str, params: Conv2dGw8Params, device, min_bytes: int) -> List[tuple]:
+    """Operand sets in the order the kernel takes them (random contents, channels_last), as many
+    as it takes for the streamed tensors to total ``min_bytes``: a timed chain rotates over them,
+    so no launch finds its operands in the L2 cache.  Weights and bias are shared."""
     cl = torch.channels_last
-    x = torch.randn(params.input_shape, device=device).half().contiguous(memory_format=cl)
-    dy = torch.randn(params.output_shape, device=device).half().contiguous(memory_format=cl)
     w = torch.randn(params.weight_shape, device=device).half().contiguous(memory_format=cl)
-    if kernel_name.endswith("fprop"):
-        bias = torch.randn(params.k, device=device) if params.has_bias else None
-        return (torch.empty_like(dy), x, w, bias)
-    if kernel_name.endswith("dgrad"):
-        return (torch.empty_like(x), dy, w, None)
-    dw = torch.empty(params.weight_shape, device=device, dtype=torch.float32).contiguous(memory_format=cl)
-    return (dw, x, dy)
+    bias = torch.randn(params.k, device=device) if params.has_bias else None
+    per_set = 2 * (params.n * params.c * params.h * params.w + params.n * params.k * params.p * params.q)
+    sets = max(2, -(-min_bytes // per_set))
+    out = []
+    for _ in range(sets):
+        x = torch.randn(params.input_shape, device=device).half().contiguous(memory_format=cl)
+        dy = torch.randn(params.output_shape, device=device).half().contiguous(memory_format=cl)
+        if kernel_name.endswith("fprop"):
+            out.append((torch.empty_like(dy), x, w, bias))
+        elif kernel_name.endswith("dgrad"):
+            out.append((torch.empty_like(x), dy, w, None))
+        else:
+            dw = torch.empty(params.weight_shape, device=device, dtype=torch.float32).contiguous(memory_format=cl)
+            out.append((dw, x, dy))
+    return out
 
 
-def time_kernel(kernel, args, reps: int = 7, flush: Optional[torch.Tensor] = None) -> float:
-    """Median milliseconds of one launch; ``flush`` (a buffer larger than L2) is rewritten
-    before every timed launch when the operands themselves do not exceed the cache."""
-    for _ in range(2):
-        kernel(*args)
+def time_kernel(kernel, operand_sets: List[tuple], reps: int = 3, target_ms: float = 1.0) -> float:
+    """Median milliseconds per launch in chains of back-to-back launches over rotating operand
+    sets: the way the kernels run in a training step (programmatic dependent launch lets a
+    launch's prologue overlap its predecessor's tail), with a cold L2 for every launch."""
+    k = len(operand_sets)
+    for i in range(2):
+        kernel(*operand_sets[i % k])
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    kernel(*operand_sets[0])
+    stop.record()
+    stop.synchronize()
+    count = max(4, min(24, int(target_ms / max(start.elapsed_time(stop), 1e-3))))
     times = []
     for _ in range(reps):
-        if flush is not None:
-            flush.zero_()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        kernel(*args)
+        for i in range(count):
+            kernel(*operand_sets[i % k])
         stop.record()
         stop.synchronize()
-        times.append(start.elapsed_time(stop))
+        times.append(start.elapsed_time(stop) / count)
     return statistics.median(times)
 
 
 def tune(kernel_name: str, params: Conv2dGw8Params, device="cuda", max_configs: int = 0,
-         reps: int = 7) -> List[Tuple[float, object]]:
+         reps: int = 3) -> List[Tuple[float, object]]:
     """(milliseconds, config) for every configuration, fastest first."""
     factory, kwargs = KERNELS[kernel_name]
     device = torch.device(device)
@@ -81,17 +97,13 @@ def tune(kernel_name: str, params: Conv2dGw8Params, device="cuda", max_configs: 
     if max_configs and len(configs) > max_configs:
         step = len(configs) / max_configs
         configs = [configs[int(i * step)] for i in range(max_configs)]
-    args = make_args(kernel_name, params, device)
-    nbytes = sum(a.numel() * a.element_size() for a in args if a is not None)
-    flush = None
-    if nbytes < 2 * attr.l2_cache_size:
-        flush = torch.empty(2 * max(attr.l2_cache_size, 64 << 20), dtype=torch.uint8, device=device)
+    sets = make_operand_sets(kernel_name, params, device, min_bytes=4 * attr.l2_cache_size)
     rows = []
     for cfg in configs:
         kernel = factory.make_kernel(params, cfg, attr, **kwargs)
         kernel.compile(attr)
         kernel.load(ordinal)
-        rows.append((time_kernel(kernel, args, reps=reps, flush=flush), cfg))
+        rows.append((time_kernel(kernel, sets, reps=reps), cfg))
     if device_status() != 0:
         raise RuntimeError("a kernel reported a wait time-out while tuning")
     rows.sort(key=lambda r: r[0])
@@ -121,6 +133,27 @@ def fit_models(rows_by_kernel: Dict[str, List[Dict[str, float]]], out_dir: Path)
         (out_dir / f"model__{name}__sm_100a.json").write_text(json.dumps(model.to_json()) + "\n")
 
 
+def read_rows(path: Path) -> Dict[str, List[Dict[str, float]]]:
+    """Timing rows written by ``--rows``, grouped by kernel."""
+    out: Dict[str, List[Dict[str, float]]] = {}
+    with Path(path).open(newline="") as fh:
+        for row in csv.DictReader(fh):
+            name = row.pop("kernel")
+            out.setdefault(name, []).append({k: float(v) for k, v in row.items()})
+    return out
+
+
+def shapes_from_file(path: Path, max_batch: int = 0) -> List[Conv2dGw8Params]:
+    """Layer shapes from a JSON list of {n, c, h, w, r, s, pad_h, pad_w, has_bias} records (the
+    format of tests/golden/model_shapes.json)."""
+    out = []
+    for d in json.loads(Path(path).read_text()):
+        n = min(d["n"], max_batch) if max_batch else d["n"]
+        out.append(Conv2dGw8Params(n=n, c=d["c"], h=d["h"], w=d["w"], r=d["r"], s=d["s"],
+                                   padding=(d["pad_h"], d["pad_w"]), has_bias=bool(d["has_bias"])))
+    return out
+
+
 def parse_shape(text: str) -> Conv2dGw8Params:
     """``n,c,h,w[,r,s,pad[,bias]]``."""
     v = [int(t) for t in text.split(",")]
@@ -132,7 +165,10 @@ def parse_shape(text: str) -> Conv2dGw8Params:
 
 def main(argv: Optional[Iterable[str]] = None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--shape", action="append", required=True, help="n,c,h,w[,r,s,pad[,bias]]")
+    ap.add_argument("--shape", action="append", default=[], help="n,c,h,w[,r,s,pad[,bias]]")
+    ap.add_argument("--shapes-file", default=None, help="JSON list of layer shapes (tests/golden/model_shapes.json)")
+    ap.add_argument("--from-rows", default=None,
+                    help="fit the models from a CSV written by --rows (no GPU needed) and exit")
     ap.add_argument("--kernel", action="append", choices=sorted(KERNELS), help="default: all three")
     ap.add_argument("--out", default=str(MODEL_DIR), help="directory of the tuning tables / models")
     ap.add_argument("--rows", default=None, help="append every measurement to this CSV")
@@ -142,10 +178,21 @@ def main(argv: Optional[Iterable[str]] = None) -> None:
 
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
+    if args.from_rows:
+        fit_models(read_rows(Path(args.from_rows)), out_dir)
+        return
     cache = PerformanceModelCache()
     rows_by_kernel: Dict[str, List[Dict[str, float]]] = {}
-    for text in args.shape:
-        params = parse_shape(text)
+    shapes = [parse_shape(text) for text in args.shape]
+    if args.shapes_file:
+        shapes += shapes_from_file(Path(args.shapes_file))
+    if not shapes:
+        ap.error("give --shape and / or --shapes-file")
+    seen = set()
+    for params in shapes:
+        if params.encode() in seen:
+            continue
+        seen.add(params.encode())
         for name in args.kernel or sorted(KERNELS):
             ranked = tune(name, params, max_configs=args.max_configs)
             best_ms, best_cfg = ranked[0]

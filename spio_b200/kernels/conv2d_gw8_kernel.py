@@ -18,6 +18,7 @@ takes ncb, ns and nob only.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import asdict, dataclass, replace
 from typing import Iterator, List
 
@@ -117,8 +118,10 @@ def _get_configs(params: Conv2dGw8Params, device_attr, igrad: bool = False) -> I
                     cfg = Conv2dGw8Config(wpg=wpg, tpw=tpw, pps=pps, ncb=ncb, nb=nb, ns=ns, nob=nob)
                     if plan_is_valid(kind, params, cfg.as_tune(), device_attr, SMEM_SOFT_CAP if ns else 0):
                         yield cfg
-    if params.r <= 3 and params.s <= 3:
-        # the tcgen05 kernel: column tiles of up to 64 - (s - 1) pixels, ring depth, staging buffers
+    if params.r <= 3 and params.s <= 3 and os.environ.get("SPIO_TUNE_TCGEN05", "0") == "1":
+        # the tcgen05 kernel: column tiles of up to 64 - (s - 1) pixels, ring depth, staging buffers.
+        # It lost on every measured shape, so it is enumerated only on request (SPIO_TUNE_TCGEN05=1);
+        # an explicit Conv2dGw8Config(engine=2) still selects it.
         for n_ct in range(1, 4):
             ncb = divup(divup(out_w, 8), n_ct)
             for ns in (0, 4, 6):

@@ -1,0 +1,80 @@
+// Host-side checks of the typed-dimension header (spio_b200/csrc/typed.h) against types generated
+// from the @spio blocks below; compiled with g++ by tests/test_generators.py.  In the spirit of the
+// reference's tutorial lessons (spio/src_tests/tutorial/01_commutativity.cpp ... 05_compound_index.cpp):
+// type safety, position-free subscripting, folding, compound indices.
+/*@spio
+I = Dim()
+J = Dim()
+K = Dim()
+K8 = Fold(K, 8)
+A = Tensor(dtype.float, Dims(I(16), K(32)))
+B = Tensor(dtype.float, Dims(K(32), J(64)))
+Folded = Tensor(dtype.float, Dims(I(4), K8(4), K(8)), Strides(K8=9))
+Threads = CompoundIndex(Dims(I(4), K8(2), J(16)))
+@spio*/
+#include <cstdio>
+#include <type_traits>
+
+#include "types.h"
+
+#define CHECK(cond)                                                   \
+  do {                                                                \
+    if (!(cond)) {                                                    \
+      std::printf("FAILED line %d: %s\n", __LINE__, #cond);          \
+      return 1;                                                       \
+    }                                                                 \
+  } while (0)
+
+template <class X, class Y, class = void>
+struct comparable : std::false_type {};
+template <class X, class Y>
+struct comparable<X, Y, std::void_t<decltype(std::declval<X>() == std::declval<Y>())>> : std::true_type {};
+
+template <class T, class Idx, class = void>
+struct subscriptable : std::false_type {};
+template <class T, class Idx>
+struct subscriptable<T, Idx, std::void_t<decltype(T::offset_of(std::declval<Idx>()))>> : std::true_type {};
+
+int main() {
+  // dimensions behave like integers, each is a type of its own, and they do not mix
+  static_assert(I(2) + I(4) == I(6));
+  static_assert(I(8) < I(10));
+  static_assert(!std::is_same_v<I, J>);
+  static_assert(comparable<I, I>::value && !comparable<I, J>::value);
+
+  // tensors know their sizes
+  static_assert(A::size<I>() == I(16) && A::size<K>() == K(32) && B::size<J>() == J(64));
+  static_assert(A::storage_size() == 16 * 32 && B::storage_size() == 32 * 64);
+  float a_data[A::storage_size()], b_data[B::storage_size()];
+  const A a(a_data);
+  const B b(b_data);
+
+  // position-free subscripting: the order of subscripts does not change the element
+  CHECK(a[I(2)][K(4)].get() == a[K(4)][I(2)].get());
+  CHECK(b[K(4)][J(3)].get() == b[J(3)][K(4)].get());
+  CHECK(a[I(2)][K(4)].get() == a_data + 2 * 32 + 4);
+  // offset_of() on a dimension the tensor lacks does not compile (checked through SFINAE here)
+  static_assert(subscriptable<A, I>::value && subscriptable<A, K>::value);
+
+  // folding: K8 counts K in blocks of 8
+  static_assert(K(19).fold<8>() == K8(2));
+  static_assert(K(19).rem<8>() == K(3));
+  static_assert(K8(2).unfold() == K(16));
+  static_assert(K8(2) + K(3) == K(19));
+  // a tensor with a folded axis whose rows are padded to 9 floats: a folded index moves along the
+  // folded axis, an unfolded one is split into fold and remainder
+  static_assert(Folded::storage_size() == 3 * 36 + 3 * 9 + 7 + 1);
+  float f_data[Folded::storage_size()];
+  const Folded f(f_data);
+  CHECK(f[I(1)][K8(2)][K(3)].get() == f_data + 36 + 2 * 9 + 3);
+  CHECK(f[I(1)][K(19)].get() == f[I(1)][K8(2)][K(3)].get());
+
+  // compound index: a linear thread index split into typed coordinates
+  static_assert(Threads::size() == 4 * 2 * 16);
+  const Threads t(1 * 32 + 1 * 16 + 5);
+  CHECK(t.get<I>() == I(1));
+  CHECK(t.get<K8>() == K8(1));
+  CHECK(t.get<J>() == J(5));
+  std::puts("typed lessons ok");
+  return 0;
+}

@@ -14,9 +14,13 @@ operands with the keyword arguments the reference derives from its Params
 (spio/src_tests/run_test.py:43-50, 84-102).  Operands follow the reference's test
 distribution, randn clipped to +-3 (spio/reflection/arg_info.py:81-85).
 
-Outputs: ``gw8_cases.npz`` (operands and expected results of small cases) and
-``gw8_params_stats.json`` (derived shapes, encoded names and statistics).
-The tests read only those two files; they never read the reference checkout.
+Outputs: ``gw8_cases.npz`` (operands and expected results of small cases),
+``gw8_params_stats.json`` (derived shapes, encoded names and statistics) and
+``model_shapes.json``: the layer shapes of real models the reference keeps for its tests and
+its performance models (spio/src_tests/Conv2dGw8Params.dat, one ``Conv2dGw8Params(...)`` per
+line), each evaluated with the reference's own class and stored as plain fields plus the
+encoded name.  The tests and the autotuner read only these files; they never read the
+reference checkout.
 """
 
 from __future__ import annotations
@@ -126,6 +130,18 @@ def main(root: Path) -> None:
                             bytes=st.bytes, accumulation_depths=st.accumulation_depths)
         stats.append(row)
     (HERE / "gw8_params_stats.json").write_text(json.dumps(stats, indent=1) + "\n")
+
+    shapes = []
+    for line in (root / "spio" / "src_tests" / "Conv2dGw8Params.dat").read_text().splitlines():
+        if not line.strip():
+            continue
+        params = eval(line, {"__builtins__": {}, "Conv2dGw8Params": Params})  # noqa: S307 - the reference's fixture
+        params.validate()
+        shapes.append(dict(n=params.n, c=params.c, h=params.h, w=params.w, r=params.r, s=params.s,
+                           pad_h=params.padding_h, pad_w=params.padding_w, has_bias=bool(params.has_bias),
+                           encode=params.encode()))
+    (HERE / "model_shapes.json").write_text(json.dumps(shapes, indent=0) + "\n")
+    print("wrote", len(shapes), "model shapes")
     print("wrote", HERE / "gw8_cases.npz", (HERE / "gw8_cases.npz").stat().st_size, "bytes")
 
 

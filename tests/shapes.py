@@ -43,6 +43,18 @@ MISC = [
     (Shape(6, 128, 48, 32, 3, 3, 1, 1), False),
 ]
 
+def load_model_shapes(max_batch: int = 0):
+    """The 81 real-model layer shapes of the reference (spio/src_tests/Conv2dGw8Params.dat), from the
+    fixture tests/golden/model_shapes.json that tests/golden/make_golden.py writes; ``max_batch``
+    caps the batch so that the CPU oracle finishes in seconds."""
+    import json
+    from pathlib import Path
+
+    rows = json.loads((Path(__file__).resolve().parent / "golden" / "model_shapes.json").read_text())
+    return [(Shape(min(d["n"], max_batch) if max_batch else d["n"], d["c"], d["h"], d["w"], d["r"], d["s"],
+                   d["pad_h"], d["pad_w"]), bool(d["has_bias"])) for d in rows]
+
+
 MODEL_SHAPES = [
     (Shape(4, 80, 56, 56, 5, 5, 2, 2), True),
     (Shape(4, 160, 28, 28, 5, 5, 2, 2), True),

@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 def alloc_buffers(world, capacity):
     lib = _clib.load()
     nbytes = lib.spio_dp_buffer_bytes(world, capacity)
-    assert nbytes >= 256 + 2 * world * capacity * 4
+    assert nbytes >= 256 + 2 * world * capacity * 8   # a word is {float, tag}
     bufs = []
     for _ in range(world):
         p = ctypes.c_void_p()
@@ -36,6 +36,24 @@ def alloc_buffers(world, capacity):
 
 def exchange(table, rank, world, seq, capacity):
     return _clib.DpExchange(ctypes.cast(table, ctypes.POINTER(ctypes.c_void_p)), rank, world, seq, capacity)
+
+
+def test_allreduce_of_one_rank_is_the_identity():
+    lib = _clib.load()
+    bufs, table = alloc_buffers(1, 4672)
+    a = torch.randn(4608, device="cuda:0")
+    b = torch.randn(64, device="cuda:0")
+    keep = (a.clone(), b.clone())
+    try:
+        for seq in range(3):
+            dp = exchange(table, 0, 1, seq, 4672)
+            _clib.check(lib.spio_dp_allreduce(ctypes.byref(dp), a.data_ptr(), 4608, b.data_ptr(), 64,
+                                              torch.cuda.current_stream().cuda_stream))
+        assert torch.equal(a, keep[0]) and torch.equal(b, keep[1])
+        assert capi.status() == 0
+    finally:
+        torch.cuda.synchronize()
+        lib.spio_dp_buffer_free(bufs[0])
 
 
 @pytest.mark.parametrize("world", [1, 2, 5, 8])

@@ -38,6 +38,22 @@ def test_static_scratch_matches_ordinary_entry_point_twice_in_a_row():
             rc, got = wgrad_static(xd, dyd, sh)
             assert rc == 0, _clib.last_error()
             assert capi.status() == 0
+            if call == 1:
+                # the property the entry point exists for: once the device is set up, a call takes
+                # no memory from the driver (cudaMalloc would lower the free bytes) nor from torch's
+                # allocator
+                out = torch.full_like(got, capi.DEAD_VALUE)       # allocated BEFORE the measured call
+                s = capi.cshape(sh)
+                torch.cuda.synchronize()
+                free_before, reserved_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
+                rc = _clib.load().spio_conv2d_gw8_wgrad_static(
+                    out.data_ptr(), xd.data_ptr(), dyd.data_ptr(), ctypes.byref(s), None,
+                    torch.cuda.current_stream().cuda_stream)
+                torch.cuda.synchronize()
+                assert rc == 0, _clib.last_error()
+                assert torch.cuda.mem_get_info()[0] == free_before, "the call took device memory from the driver"
+                assert torch.cuda.memory_reserved() == reserved_before, "the call took memory from torch's allocator"
+                assert torch.equal(out, expected)
             # same kernels, same fixed summation order: the results are identical
             assert torch.equal(got, expected), f"shape {i}, call {call}"
         O.assert_close(expected, O.c_wgrad(x, dy, sh), sh, "wgrad", "static scratch")
