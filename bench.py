@@ -200,6 +200,20 @@ class LayerPoint:
         self.bytes = algorithmic_bytes(n, c, hw)
 
     def c_abi(self, count: int = 40) -> dict:
+        # The kernels' time follows the SM clock at small batch, and the clock sags for a while after
+        # a long stretch of full load: let the board settle, and record the clock seen while timing.
+        torch.cuda.synchronize()
+        time.sleep(0.3)
+        sampler = ClockSampler(self.dev.index or 0, period_s=0.001)
+        sampler.start()
+        try:
+            res = self._c_abi(count)
+        finally:
+            clocks = sampler.stop()
+        res["sm_mhz"] = {k: clocks.get(k) for k in ("sm_mhz", "sm_mhz_min", "samples")}
+        return res
+
+    def _c_abi(self, count: int) -> dict:
         lib, shp, chk = self.lib, self.shp, self.clib.check
         sp = torch.cuda.current_stream(self.dev).cuda_stream
         k = self.sets
@@ -266,6 +280,40 @@ class LayerPoint:
             chosen[name] = {f: v for f, v in kern.config.as_tune().items() if v} if kern.config is not None else {}
         return {"fprop": self._rate(fwd_us), "step": dict(self._rate(step_us / 3.0), us=step_us),
                 "backward_us": step_us - fwd_us, "host_us_per_step": host_us(step, 50), "configs": chosen}
+
+    def incumbent(self, count: int = 24) -> dict:
+        """The REFERENCE's own kernels for this shape (compiled for sm_100a into oracle/_ref by
+        oracle/build_ref_kernels.py), timed in the same chains over the same rotating operands; per
+        kernel the fastest of the configurations that were built.  They are launched as the reference
+        launches them: plain cuLaunchKernel, and a zero fill of grad_weight before every wgrad."""
+        from oracle import ref_kernels
+
+        k = self.sets
+        res = {}
+        for kind in ("fprop", "dgrad", "wgrad"):
+            best = None
+            for kern in ref_kernels.kernels_for(kind, self.n, self.c, self.hw, self.hw):
+                kern.load()
+                if kind == "fprop":
+                    fn = lambda i, kern=kern: kern(self.out[i % k], self.a[i % k], self.w, None)  # noqa: E731
+                elif kind == "dgrad":
+                    fn = lambda i, kern=kern: kern(self.out[i % k], self.b[i % k], self.w)  # noqa: E731
+                else:
+                    def fn(i, kern=kern):
+                        self.dw.zero_()
+                        kern(self.dw, self.a[i % k], self.b[i % k])
+                for i in range(4):
+                    fn(i)
+                us = chain_us(fn, count, reps=3)
+                if best is None or us < best[0]:
+                    best = (us, kern.config)
+                kern.unload()
+            if best is not None:
+                res[kind] = dict(self._rate(best[0]), config=best[1])
+        if len(res) == 3:
+            us = sum(res[kind]["us"] for kind in res)
+            res["step"] = dict(self._rate(us / 3.0), us=us)
+        return res
 
     def _rate(self, us: float) -> dict:
         peak, _ = measured_peak()
@@ -517,22 +565,6 @@ def run_ours(args) -> None:
     if _clib.device_status() != 0:
         raise SystemExit("kernel status word reported a wait time-out")
 
-    # ---- sustained: a few hundred steps, long enough for the power management to settle
-    sus_steps = max(200, args.steps) if not args.no_sustained else 0
-    sus_ms, sus_clocks = float("nan"), None
-    if sus_steps:
-        s2 = ClockSampler(local_rank)
-        if rank == 0:
-            s2.start()
-        barrier()
-        t0.record(main)
-        for k in range(sus_steps):
-            step()
-        t1.record(main)
-        barrier()
-        sus_clocks = s2.stop() if rank == 0 else None
-        sus_ms = t0.elapsed_time(t1) / sus_steps
-
     # ---- second pass, outside the timed region: the same steps with an event between the
     # kernels, for the per-kernel durations (the event records themselves cost a few us per step)
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
@@ -595,6 +627,23 @@ def run_ours(args) -> None:
             dist.all_gather(parts, hdw.to(dev))
             e2e_ok = e2e_ok and all(torch.equal(parts[0], p) for p in parts)
         ceiling = copy_ceiling(dev, world, dist)
+
+    # ---- sustained: a few hundred steps, long enough for the power management to settle (after the
+    # short measurements, which it would otherwise disturb: the clock sags for a while afterwards)
+    sus_steps = max(200, args.steps) if not args.no_sustained else 0
+    sus_ms, sus_clocks = float("nan"), None
+    if sus_steps:
+        s2 = ClockSampler(local_rank)
+        if rank == 0:
+            s2.start()
+        barrier()
+        t0.record(main)
+        for k in range(sus_steps):
+            step()
+        t1.record(main)
+        barrier()
+        sus_clocks = s2.stop() if rank == 0 else None
+        sus_ms = t0.elapsed_time(t1) / sus_steps
 
     times = torch.tensor([total_ms, e2e_s * 1e3, sus_ms] + kern_ms, device=dev, dtype=torch.float64)
     if world > 1:
@@ -665,13 +714,27 @@ def run_ours(args) -> None:
             "clocks": clocks,
         }
         if world == 1 and not args.no_sweep:
-            del x, dy, y, dx
-            torch.cuda.empty_cache()
+            time.sleep(0.5)
+            incumbent_ok = False
+            if not args.no_incumbent:
+                try:
+                    from oracle import ref_kernels
+
+                    incumbent_ok = ref_kernels.available()
+                except Exception:
+                    incumbent_ok = False
+            line["incumbent_note"] = (
+                "the reference's own kernels (spio/src/conv2d_gw8.cu, conv2d_gw8_wgrad.cu) NVRTC-compiled for sm_100a "
+                "from the reference checkout, best of the built configurations per kernel, launched as the reference "
+                "launches them (no programmatic launch, zero fill before wgrad)" if incumbent_ok
+                else "oracle/_ref has not been built: no incumbent figures")
             sweep = {}
             for bn in (128, 256, 512):
                 pt = LayerPoint(lib, dev, bn, C, H, seed=1234 + 2)
                 sweep[f"n{bn}"] = {"algorithmic_bytes": pt.bytes, "operand_sets": pt.sets,
                                    "c_abi_planner_defaults": pt.c_abi(), "operator_tuned_tables": pt.operator()}
+                if incumbent_ok:
+                    sweep[f"n{bn}"]["incumbent_reference_kernels"] = pt.incumbent()
                 del pt
                 torch.cuda.empty_cache()
             line["sweep"] = sweep
@@ -685,9 +748,21 @@ def run_ours(args) -> None:
                 pt = LayerPoint(lib, dev, 256, c_, hw_, seed=1234 + 3)
                 ladder[f"c{c_}_{hw_}x{hw_}"] = {"algorithmic_bytes": pt.bytes, "operand_sets": pt.sets,
                                                 "c_abi_planner_defaults": pt.c_abi(), "operator_tuned_tables": pt.operator()}
+                if incumbent_ok:
+                    ladder[f"c{c_}_{hw_}x{hw_}"]["incumbent_reference_kernels"] = pt.incumbent()
                 del pt
                 torch.cuda.empty_cache()
             line["ladder"] = ladder
+            if incumbent_ok and global_batch == GLOBAL_BATCH:   # last: the heaviest leg
+                time.sleep(0.5)
+                pt = LayerPoint(lib, dev, global_batch, C, H, seed=1234 + 5)
+                line["incumbent"] = pt.incumbent(count=8)
+                ours_step = pt.c_abi(count=8)["step"]["us"]
+                line["incumbent"]["ours_step_us_same_protocol"] = ours_step
+                if "step" in line["incumbent"]:
+                    line["incumbent"]["speedup_of_step"] = line["incumbent"]["step"]["us"] / ours_step
+                del pt
+                torch.cuda.empty_cache()
             line["host_us_per_call"] = sweep["n256"]["c_abi_planner_defaults"]["host_us_per_call"]
             if not args.no_convnext:
                 try:
@@ -791,6 +866,7 @@ def main() -> None:
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch sweep, the ladder and the ConvNeXt step")
     ap.add_argument("--no-convnext", action="store_true", help="skip the ConvNeXt train step")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 200-step run")
+    ap.add_argument("--no-incumbent", action="store_true", help="skip the reference's own kernels")
     ap.add_argument("--collective", choices=["peer", "nccl"], default="peer",
                     help="how dw is summed over the ranks (N > 1)")
     ap.add_argument("--force-exchange", action="store_true",
