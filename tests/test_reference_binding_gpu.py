@@ -51,15 +51,20 @@ def test_model_script_written_for_the_reference_runs_under_the_spio_name():
     assert spio.supported_arch == ["sm_100a"]
     torch.manual_seed(7)
     model = torch.nn.Sequential(torch.nn.Conv2d(64, 64, 3, padding=1, groups=8), torch.nn.ReLU(),
-                                torch.nn.Conv2d(64, 64, 3, padding=1, groups=8)).cuda().half()
-    model = model.to(memory_format=torch.channels_last)
-    x = torch.randn(4, 64, 20, 20, device="cuda").half().contiguous(memory_format=torch.channels_last)
-    want = model(x)
+                                torch.nn.Conv2d(64, 64, 3, padding=1, groups=8)).cuda()
+    model = model.to(memory_format=torch.channels_last)      # fp32 parameters, fp16 under autocast
+    x = torch.randn(4, 64, 20, 20, device="cuda").contiguous(memory_format=torch.channels_last)
+    with torch.autocast("cuda", dtype=torch.float16):
+        want = model(x)
     fast = spio.transform.transform(model)
     assert sum(isinstance(m, Conv2dGw8) for m in fast.modules()) == 2
-    got = fast(x)
+    with torch.autocast("cuda", dtype=torch.float16):
+        got = fast(x)
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
-    p = Conv2dGw8Params.from_tensors(x, model[0].weight, model[0].bias, padding=1)
-    y = conv2d_gw8(x, model[0].weight, model[0].bias.float(), padding_y=1, padding_x=1, groups=p.groups)
-    torch.testing.assert_close(y.float(), model[0](x).float(), rtol=2e-2, atol=2e-2)
+    xh, wh = x.half(), model[0].weight.detach().half().contiguous(memory_format=torch.channels_last)
+    p = Conv2dGw8Params.from_tensors(xh, wh, model[0].bias, padding=1)
+    y = conv2d_gw8(xh, wh, model[0].bias.detach(), padding_y=1, padding_x=1, groups=p.groups)
+    with torch.autocast("cuda", dtype=torch.float16):
+        ref = model[0](x)
+    torch.testing.assert_close(y.float(), ref.float(), rtol=2e-2, atol=2e-2)
     assert capi.status() == 0
