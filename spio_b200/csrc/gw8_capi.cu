@@ -362,8 +362,32 @@ int dyn_pool_percent() {
   return v;
 }
 
+int make_plan_once(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
+                   const std::vector<Gw8Variant>& variants, Plan* plan, const Gw8Variant* forced);
+
+// The planner's own choice of row pairs per slot for the weight-gradient kernel: two, unless that
+// leaves a ring of only two slots (a stage holds an x box and a dy box; several images of a small
+// picture per slot make it 70-80 KiB) -- then one, which halves the stage and doubles the ring
+// (measured: 256 x 256 x 28 x 28 48.9 -> 45.5 us, 256 x 512 x 14 x 14 32.1 -> 29.6 us).
 int make_plan(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
               const std::vector<Gw8Variant>& variants, Plan* plan, const Gw8Variant* forced = nullptr) {
+  if (make_plan_once(kind, sh, tune, sms, smem_optin, variants, plan, forced)) return 1;
+  const bool open_pps = forced == nullptr && (tune == nullptr || (!tune->pps && !tune->ns && !tune->wpg && !tune->tpw));
+  if (kind == SPIO_GW8_WGRAD && open_pps && plan->ns <= 2 && plan->v != nullptr && plan->v->pps == 2) {
+    spio_gw8_tune t = tune ? *tune : spio_gw8_tune{0, 0, 0, 0, 0, 0, 0, 0, 0};
+    t.pps = 1;
+    Plan alt;
+    const std::string keep = g_last_error;
+    if (make_plan_once(kind, sh, &t, sms, smem_optin, variants, &alt, nullptr) == 0 && alt.ns >= 3)
+      *plan = alt;
+    else
+      g_last_error = keep;
+  }
+  return 0;
+}
+
+int make_plan_once(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune, int sms, int smem_optin,
+                   const std::vector<Gw8Variant>& variants, Plan* plan, const Gw8Variant* forced) {
   if (check_shape(sh)) return 1;
   static const spio_gw8_tune kAuto = {0, 0, 0, 0, 0, 0, 0, 0, 0};
   const spio_gw8_tune& t = tune ? *tune : kAuto;

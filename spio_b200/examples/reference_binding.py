@@ -14,7 +14,7 @@ import torch
 
 _LIB_PATH = os.environ.get("SPIO_B200_LIB") or os.path.join(
     os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libspio_b200.so")
-_lib = ctypes.CDLL(_LIB_PATH)
+_lib = ctypes.CDLL(_LIB_PATH)            # libspio_b200.so
 _lib.spio_conv2d_gw8_wgrad_scratch_bytes.restype = ctypes.c_size_t
 _lib.spio_b200_last_error.restype = ctypes.c_char_p
 

@@ -135,10 +135,16 @@ def test_planner_keeps_rings_inside_the_196_kib_configuration():
     assert rc == 0 and p["ns"] == 4 and p["smem_bytes"] <= cap
     rc, p = plan(_clib.DGRAD, Shape(256, 64, 56, 56, 3, 3, 1, 1), {"ns": 5})
     assert rc == 0 and p["ns"] == 5 and p["smem_bytes"] > cap
+    # two row pairs per slot would leave the weight-gradient ring two slots deep under the cap:
+    # the planner then streams one row pair per slot, which fits five
     rc, p = plan(_clib.WGRAD, Shape(256, 256, 28, 28, 3, 3, 1, 1))
+    assert rc == 0 and p["pps"] == 1 and p["ns"] == 5 and p["smem_bytes"] <= cap
+    rc, p = plan(_clib.WGRAD, Shape(256, 256, 28, 28, 3, 3, 1, 1), {"pps": 2})
     assert rc == 0 and p["ns"] == 2 and p["smem_bytes"] <= cap
-    rc, p = plan(_clib.WGRAD, Shape(256, 256, 28, 28, 3, 3, 1, 1), {"ns": 3})
+    rc, p = plan(_clib.WGRAD, Shape(256, 256, 28, 28, 3, 3, 1, 1), {"pps": 2, "ns": 3})
     assert rc == 0 and p["ns"] == 3 and p["smem_bytes"] > cap
+    rc, p = plan(_clib.WGRAD, Shape(256, 64, 56, 56, 3, 3, 1, 1))
+    assert rc == 0 and p["pps"] == 2 and p["ns"] == 3
     # three slots of the 14 x 14 forward plan do not fit under the cap: the floor wins
     rc, p = plan(_clib.FPROP, Shape(256, 512, 14, 14, 3, 3, 1, 1))
     assert rc == 0 and p["ns"] == 3 and p["smem_bytes"] > cap
