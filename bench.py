@@ -418,19 +418,36 @@ def run_ours(args) -> None:
     sp = main.cuda_stream
 
     # ---- the collective: peer-store exchange inside the launch chain, else NCCL on a side stream
-    px, collective = None, "none (1 GPU)"
+    px, px_all, collective = None, None, "none (1 GPU)"
     if world > 1:
         collective = "nccl all-reduce on a side stream, overlapped with dgrad"
         if args.collective == "peer":
             try:
-                px = PeerExchange(C * 8 * R * S + C, device=dev)
+                px = px_all = PeerExchange(C * 8 * R * S + C, device=dev)
                 collective = "peer-store exchange inside the launch chain (spio_dp_push / spio_dp_sum)"
             except Exception as exc:  # IPC not available here: the NCCL route still works
                 collective += f" (peer exchange unavailable: {exc})"
+        if px is not None:
+            # trial run: the exchange must give the bits of a rank-order sum (checked against NCCL's sum
+            # of the same vector, which may differ in the last bit) before the timed steps rely on it
+            try:
+                probe = torch.randn(C * 8 * R * S, device=dev)
+                want = probe.clone()
+                dist.all_reduce(want)
+                for _ in range(3):
+                    got = probe.clone()
+                    dp = px.options()
+                    _clib.check(lib.spio_dp_allreduce(ctypes.byref(dp), got.data_ptr(), got.numel(), None, 0, sp))
+                    px.advance()
+                    torch.cuda.synchronize(dev)
+                    if _clib.device_status() != 0 or not torch.allclose(got, want, rtol=1e-5, atol=1e-5):
+                        raise RuntimeError("trial exchange gave a wrong sum or timed out")
+            except Exception as exc:
+                collective += f" (peer exchange rejected: {exc})"
+                px = None   # the buffers stay mapped until the end: peers may still be storing into them
         ok = torch.tensor([1 if px is not None else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if int(ok.item()) == 0 and px is not None:   # all ranks must agree on the route
-            px.close()
             px = None
             collective = "nccl all-reduce on a side stream, overlapped with dgrad (peer exchange failed on a rank)"
     if world == 1 and args.force_exchange:   # one rank exchanging with itself: the cost of the chain alone
@@ -773,9 +790,9 @@ def run_ours(args) -> None:
                 raise SystemExit("kernel status word reported a wait time-out in the sweeps")
         line["cpu_baseline"] = cpu_baseline(max_seconds=20.0) if world == 1 and not args.no_cpu else None
         print(json.dumps(line), flush=True)
-    if px is not None:
+    if px_all is not None or px is not None:
         barrier()
-        px.close()
+        (px_all or px).close()
     if world > 1:
         dist.destroy_process_group()
 

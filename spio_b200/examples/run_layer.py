@@ -21,7 +21,8 @@ from spio_b200 import _clib
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kind", choices=["fprop", "dgrad", "wgrad"])
+    ap.add_argument("kind", choices=["fprop", "dgrad", "wgrad", "layernorm"],
+                    help="layernorm = forward + backward of spio::layernorm_2d on an n x c x hw x hw tensor")
     ap.add_argument("n", type=int)
     ap.add_argument("c", type=int)
     ap.add_argument("hw", type=int)
@@ -36,6 +37,18 @@ def main() -> None:
     dev = torch.device("cuda:0")
     cl = torch.channels_last
     n, c, hw, r = args.n, args.c, args.hw, args.filter
+    if args.kind == "layernorm":
+        from spio_b200.functional import layernorm_2d_backward_op, layernorm_2d_op
+
+        gen = torch.Generator(device=dev).manual_seed(1234)
+        weight, bias = torch.randn(c, device=dev, generator=gen), torch.randn(c, device=dev, generator=gen)
+        xs = [torch.randn(n, c, hw, hw, device=dev, generator=gen).half().contiguous(memory_format=cl) for _ in range(3)]
+        for i in range(args.launches):
+            y, stats = layernorm_2d_op(xs[i % 3], weight, bias, 1e-6)
+            layernorm_2d_backward_op(xs[(i + 1) % 3], xs[i % 3], stats, weight, True, True)
+        torch.cuda.synchronize()
+        print(f"layernorm {n}x{c}x{hw}x{hw}: {args.launches} forward + backward launches ok")
+        return
     sh = _clib.Shape(n, c, hw, hw, r, r, r // 2, r // 2)
     shp = ctypes.byref(sh)
     tune = _clib.make_tune(json.loads(args.tune)) if args.tune else None
