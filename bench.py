@@ -260,9 +260,11 @@ class LayerPoint:
         w = self.w.detach().requires_grad_(True)
         groups = self.c // 8
 
+        keep = [None] * k   # outputs stay alive, as activations do in a network: the allocator hands out k buffers in turn
+
         def fwd(i):
             with torch.no_grad():
-                conv2d_gw8(xs[i % k], w, None, 1, PAD, PAD, 1, groups)
+                keep[i % k] = conv2d_gw8(xs[i % k], w, None, 1, PAD, PAD, 1, groups)
 
         def step(i):
             y = conv2d_gw8(xs[i % k], w, None, 1, PAD, PAD, 1, groups)

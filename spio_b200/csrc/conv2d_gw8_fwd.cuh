@@ -122,6 +122,7 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
         int slot = 0;
         u32 par = 0;
         bool ok = true;
+        int issued = 0;  // stages issued so far, counted only until the start-up window has been passed
         auto load_span = [&](int ua, int ub) {
           Gw8Walk walk(ua, ub, g);
           Gw8Segment seg;
@@ -132,6 +133,14 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
             const int w0 = seg.ct * g.wt - g.pad_w;
             const int n0 = seg.ig * g.nb;
             for (int i = 0; i < nst; ++i) {
+              if (issued >= 0 && g.prefill > 0 && issued++ == g.prefill) {
+                // start-up window: let the first slot land before the rest of the ring is requested
+                issued = -1;
+                if (!mbar_wait(full(0), 0u, abortp)) {
+                  ok = false;
+                  break;
+                }
+              }
               if (!mbar_wait(empty(slot), par ^ 1u, abortp)) {
                 ok = false;
                 break;

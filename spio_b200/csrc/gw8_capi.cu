@@ -342,6 +342,17 @@ int dyn_chunk_setting() {
   return v;
 }
 
+// Stages requested at kernel start before the load lane waits for the first to land
+// (Gw8Geom::prefill); SPIO_PREFILL=<n> changes it, 0 requests the whole ring at once.
+int prefill_setting() {
+  static const int v = [] {
+    const char* e = getenv("SPIO_PREFILL");
+    const int n = e ? atoi(e) : 2;
+    return n >= 0 && n <= 16 ? n : 2;
+  }();
+  return v;
+}
+
 // Pairs per CTA from which the dynamic tail is used.
 int dyn_min_pairs() {
   static const int v = [] {
@@ -529,6 +540,9 @@ int make_plan_once(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune
     else
       return fail("tile does not fit in shared memory");
   }
+  // the start-up window pays on the forward kernel's ordinary layout only: measured, it gains about
+  // 0.7 us per launch there, loses as much on paired 7x7 images and does nothing for the weight gradient
+  g.prefill = fwd && !pair && prefill_setting() < pl.ns ? prefill_setting() : 0;
   g.nblk = cdiv(g.wt, 16);
   g.ntiles = pair ? g.nb / 2 : g.nb * tiles_needed(g.ncb);
   g.pair_images = pair ? 1 : 0;

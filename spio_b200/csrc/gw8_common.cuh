@@ -66,6 +66,11 @@ struct Gw8Geom {
   int dyn_slot;        // which pair of counters behind the status word this launch uses
   int hint_in;         // L2 eviction hint (L2_HINT_*) for loads of the streamed operand
   int hint_tiled;      // wgrad: the same for loads of dy
+  int prefill;         // stages the load lane issues at kernel start before it waits for the first one to
+                       // land (0 = no limit).  With the whole ring requested at once, every CTA's first
+                       // slot competes with its later slots (and all other CTAs') for the memory system
+                       // and lands after about 3 us; requested with one companion it lands in about half
+                       // that, and the compute warps start that much earlier.
   int chunk_inner;     // fprop/dgrad: order of the flattened work.  0: chunk, image group, column
                        // tile, pair (a CTA stays in one 64-channel chunk); 1: image group, column
                        // tile, chunk, pair (a CTA does all chunks of an image one after the other,

@@ -250,16 +250,24 @@ layernorm_2d_bwd_kernel(uint4* __restrict__ dx, float* __restrict__ part, const 
   }
 }
 
-// dweight[c] / dbias[c] = sum over CTAs of the partials, in a fixed order.
+// dweight[c] / dbias[c] = sum over CTAs of the partials, in a fixed order: one warp per output
+// value, lane l adds the partials l, l + 32, ... and the 32 lane sums are combined by a shuffle tree.
+// (One thread per value walking all ~600 partials one after the other took 45 us, a third of the
+// backward pass of a 96-channel layer.)
 __global__ void __launch_bounds__(256)
 layernorm_2d_bwd_reduce_kernel(float* __restrict__ dweight, float* __restrict__ dbias,
                                const float* __restrict__ part, int c, int n_parts) {
   grid_dependency_launch_dependents();
   grid_dependency_wait();
-  const int e = blockIdx.x * 256 + threadIdx.x;
+  const int e = (blockIdx.x * 256 + threadIdx.x) >> 5;  // the same for all lanes of a warp
+  const int lane = threadIdx.x & 31;
   if (e >= 2 * c) return;
   float s = 0.f;
-  for (int p = 0; p < n_parts; ++p) s += __ldcg(part + (size_t)p * 2 * c + e);
+#pragma unroll 4
+  for (int p = lane; p < n_parts; p += 32) s += __ldcg(part + (size_t)p * 2 * c + e);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+  if (lane != 0) return;
   if (e < c) {
     if (dweight != nullptr) dweight[e] = s;
   } else if (dbias != nullptr) {
@@ -361,7 +369,7 @@ int spio_layernorm_2d_bwd(void* dx, float* dweight, float* dbias, const void* dy
   int n_parts = p.grid;
   void* rargs[] = {&dweight, &dbias, &part, &c, &n_parts};
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((2 * c + 255) / 256);
+  cfg.gridDim = dim3((2 * c + 7) / 8);  // eight warps per CTA, one warp per output value
   cfg.blockDim = dim3(256);
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];
