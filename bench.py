@@ -21,7 +21,10 @@ Extra keys of the line (single-GPU run): ``sustained`` (>= 200 steps with the sa
 ``sweep`` (the batch sweep of the 64-channel 56x56 layer at N = 128, 256, 512: per kernel through
 the C ABI with the planner's defaults, and through the PyTorch operator, which takes its tile
 configurations from the tuning tables), ``ladder`` (the channel / resolution ladder at N = 256),
-``convnext_step_ms`` (the ConvNeXt-T-style train step at batch 256) and ``host_us_per_call``.
+``convnext_step_ms`` (the ConvNeXt-T-style train step at batch 256, and the same network as stock
+torch runs it) and ``host_us_per_call``.  Each sweep / ladder point also carries the incumbents
+on the same operands: the reference's own kernels (when oracle/_ref was built) and torch's
+grouped convolution through cuDNN.
 Kernels of the sweep and the ladder are timed in chains of back-to-back launches that rotate
 over operand sets totalling more than 600 MB, so every launch finds a cold L2.
 """
@@ -242,6 +245,17 @@ class LayerPoint:
                 fn(i)
             us = chain_us(fn, count)
             res[name] = self._rate(us)
+        def backward(i):
+            chk(lib.spio_conv2d_gw8_backward(self.out[i % k].data_ptr(), self.dw.data_ptr(), None,
+                                             self.a[i % k].data_ptr(), self.b[i % k].data_ptr(), self.w.data_ptr(),
+                                             shp, None, None, self.scratch.data_ptr(), self.scratch_bytes, sp, None))
+
+        # wgrad -> reduce -> dgrad as the operator's backward pass issues them: the input-gradient kernel does
+        # not wait for the reduction, which costs a chain of bare wgrad + reduce launches about 4 us per launch
+        for i in range(8):
+            backward(i)
+        us = chain_us(backward, count // 2)
+        res["backward"] = dict(self._rate(us / 2.0), us=us)
         for i in range(8):
             step(i)
         us = chain_us(step, count // 2)
@@ -317,15 +331,48 @@ class LayerPoint:
             res["step"] = dict(self._rate(us / 3.0), us=us)
         return res
 
+    def cudnn(self, count: int = 20) -> dict:
+        """torch's own grouped convolution (cuDNN, fp16, channels_last, algorithm search on) on the same
+        rotating operands: forward alone, and forward + autograd of input and weight."""
+        import torch.nn.functional as F
+
+        k = self.sets
+        groups = self.c // 8
+        xs = [t.detach().requires_grad_(True) for t in self.a]
+        w = self.w.detach().requires_grad_(True)
+        keep = [None] * k
+        was = torch.backends.cudnn.benchmark
+        torch.backends.cudnn.benchmark = True
+
+        def fwd(i):
+            with torch.no_grad():
+                keep[i % k] = F.conv2d(xs[i % k], w, None, 1, PAD, 1, groups)
+
+        def step(i):
+            y = F.conv2d(xs[i % k], w, None, 1, PAD, 1, groups)
+            torch.autograd.grad(y, (xs[i % k], w), self.b[i % k])
+
+        try:
+            for i in range(3):
+                fwd(i)
+                step(i)
+            fwd_us = chain_us(fwd, count, reps=3)
+            step_us = chain_us(step, count, reps=3)
+        finally:
+            torch.backends.cudnn.benchmark = was
+        return {"fprop": self._rate(fwd_us), "step": dict(self._rate(step_us / 3.0), us=step_us),
+                "backward_us": step_us - fwd_us}
+
     def _rate(self, us: float) -> dict:
         peak, _ = measured_peak()
         gbs = self.bytes / us / 1e3
         return {"us": us, "GBps": gbs, "frac_of_measured_peak": gbs / peak}
 
 
-def convnext_step_ms(dev, batch: int = 256, steps: int = 5) -> dict:
+def convnext_step_ms(dev, batch: int = 256, steps: int = 5, stock: bool = False) -> dict:
     """Train step (forward + backward, fp16 autocast) of the ConvNeXt-T-style network with its 18
-    gw8 convolutions and 22 channel LayerNorms swapped for this package's layers."""
+    gw8 convolutions and 22 channel LayerNorms swapped for this package's layers; with ``stock`` the
+    same network as torch builds it (cuDNN grouped convolutions, torch's LayerNorm), for comparison."""
     from spio_b200.examples.convnext_gw8 import ConvNeXtGw8, swap_layernorm, train_step
     from spio_b200.transform._transform import _transform
 
@@ -333,8 +380,12 @@ def convnext_step_ms(dev, batch: int = 256, steps: int = 5) -> dict:
     model = ConvNeXtGw8().to(dev).to(memory_format=CL)
     images = torch.randn(batch, 3, 224, 224, device=dev).contiguous(memory_format=CL)
     labels = torch.randint(0, 1000, (batch,), device=dev)
-    n_ln = swap_layernorm(model)
-    fused, n_conv = _transform(model)
+    if stock:
+        fused, n_conv, n_ln = model, 0, 0
+        torch.backends.cudnn.benchmark = True
+    else:
+        n_ln = swap_layernorm(model)
+        fused, n_conv = _transform(model)
     for _ in range(3):
         fused.zero_grad(set_to_none=True)
         train_step(fused, images, labels)
@@ -754,11 +805,14 @@ def run_ours(args) -> None:
                                    "c_abi_planner_defaults": pt.c_abi(), "operator_tuned_tables": pt.operator()}
                 if incumbent_ok:
                     sweep[f"n{bn}"]["incumbent_reference_kernels"] = pt.incumbent()
+                if not args.no_incumbent:
+                    sweep[f"n{bn}"]["incumbent_torch_cudnn"] = pt.cudnn()
                 del pt
                 torch.cuda.empty_cache()
             line["sweep"] = sweep
             line["sweep_note"] = ("C=K=64 56x56 3x3 layer; us per launch in a chain of back-to-back launches rotating "
-                                  "over operand sets > 600 MB (cold L2), programmatic dependent launch on; 'step' is "
+                                  "over operand sets > 600 MB (cold L2), programmatic dependent launch on; 'backward' is "
+                                  "the combined call (wgrad, reduce, dgrad; rate over the bytes of two kernels); 'step' is "
                                   "fprop + combined backward, its rate counts the bytes of three kernels; operator = "
                                   "torch.ops.spio.conv2d_gw8 + autograd with the tuning-table configurations, timed on "
                                   "the device with the host queued ahead")
@@ -769,6 +823,8 @@ def run_ours(args) -> None:
                                                 "c_abi_planner_defaults": pt.c_abi(), "operator_tuned_tables": pt.operator()}
                 if incumbent_ok:
                     ladder[f"c{c_}_{hw_}x{hw_}"]["incumbent_reference_kernels"] = pt.incumbent()
+                if not args.no_incumbent:
+                    ladder[f"c{c_}_{hw_}x{hw_}"]["incumbent_torch_cudnn"] = pt.cudnn()
                 del pt
                 torch.cuda.empty_cache()
             line["ladder"] = ladder
@@ -786,6 +842,8 @@ def run_ours(args) -> None:
             if not args.no_convnext:
                 try:
                     line["convnext_step_ms"] = convnext_step_ms(dev)
+                    if not args.no_incumbent:
+                        line["convnext_step_ms"]["stock_torch_ms"] = convnext_step_ms(dev, stock=True)["ms"]
                 except Exception as exc:  # the headline must not depend on the example model
                     line["convnext_step_ms"] = {"error": str(exc)[:200]}
             if _clib.device_status() != 0:

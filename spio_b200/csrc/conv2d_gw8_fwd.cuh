@@ -79,6 +79,26 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   // Everything above touches only shared memory and may overlap the tail of the preceding
   // kernel.  Dependents are released only after the wait, so a chain of such launches never
   // runs ahead of the work that precedes its first kernel.
+  // A segment of L pairs is streamed in ceil((L + E) / PPS) stages.  Stage i brings the
+  // input row pairs PPS*i .. PPS*i+PPS-1 (relative to the segment) and completes the
+  // output pairs PPS*i+u-E, u < PPS, that lie in [0, L).  The load warp and the store
+  // lanes walk the CTA's span; the compute warps are told what a slot holds by the
+  // descriptor the load warp writes next to it.
+  auto stages_of = [&](const Gw8Segment& sg) { return (sg.m1 - sg.m0 + E + PPS - 1) / PPS; };
+  const int total = g.n_chunks * g.n_ig * g.n_ct * g.n_pairs;
+  const int n_static = g.dyn_chunk > 0 ? g.dyn_begin : total;
+  if (threadIdx.x == 32 * NCW && g.warm > 0 && !g.independent) {
+    // The load lane asks L2 for the boxes of its first stages while the preceding kernel drains.
+    Gw8Walk walk(gw8_span_begin(n_static, blockIdx.x, gridDim.x), gw8_span_begin(n_static, blockIdx.x + 1, gridDim.x), g);
+    Gw8Segment seg;
+    int left = g.warm;
+    while (left > 0 && walk.next(seg)) {
+      const int nst = stages_of(seg);
+      for (int i = 0; i < nst && left > 0; ++i, --left)
+        tma_prefetch_4d(&in_map, seg.ck * 64, seg.ct * g.wt - g.pad_w, 2 * (seg.m0 + PPS * i) - g.pad_h,
+                        seg.ig * g.nb);
+    }
+  }
   if (!g.independent) grid_dependency_wait();
   grid_dependency_launch_dependents();
 
@@ -86,12 +106,6 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
   const int lane = threadIdx.x & 31;
   volatile int* abortp = &abort_flag;
 
-  // A segment of L pairs is streamed in ceil((L + E) / PPS) stages.  Stage i brings the
-  // input row pairs PPS*i .. PPS*i+PPS-1 (relative to the segment) and completes the
-  // output pairs PPS*i+u-E, u < PPS, that lie in [0, L).  The load warp and the store
-  // lanes walk the CTA's span; the compute warps are told what a slot holds by the
-  // descriptor the load warp writes next to it.
-  auto stages_of = [&](const Gw8Segment& sg) { return (sg.m1 - sg.m0 + E + PPS - 1) / PPS; };
   auto out_mask = [&](int i, int len) {
     int m = 0;
 #pragma unroll
@@ -110,8 +124,6 @@ conv2d_gw8_fwd_body(const TensorMap& in_map, const TensorMap& out_map, const Gw8
     // claim from in pieces of g.dyn_chunk pairs, so that CTAs whose HBM traffic was served
     // faster take more of the tail.  The load lane publishes every piece it claims in `dynq`
     // for the store lanes, which walk the same sequence.
-    const int total = g.n_chunks * g.n_ig * g.n_ct * g.n_pairs;
-    const int n_static = g.dyn_chunk > 0 ? g.dyn_begin : total;
     const int u0 = gw8_span_begin(n_static, blockIdx.x, gridDim.x);
     const int u1 = gw8_span_begin(n_static, blockIdx.x + 1, gridDim.x);
     if (warp == NCW) {

@@ -80,9 +80,6 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
   // Everything above touches only shared memory and may overlap the tail of the preceding
   // kernel.  Dependents are released only after the wait, so a chain of such launches never
   // runs ahead of the work that precedes its first kernel.
-  if (!g.independent) grid_dependency_wait();
-  grid_dependency_launch_dependents();
-
   // CTA b works on split `si` of chunks cl, cl + chunk_step, ...
   const int si = blockIdx.x % g.n_split;
   const int cl = blockIdx.x / g.n_split;
@@ -99,6 +96,24 @@ conv2d_gw8_wgrad_body(const TensorMap& x_map, const TensorMap& dy_map, const Gw8
   // in sub-step u if it lies in [0, L).
   auto stages_of = [&](const Gw8Segment& sg) { return (sg.m1 - sg.m0 + E + PPS - 1) / PPS; };
   auto stage_has_pairs = [&](int i) { return PPS * i + PPS - 1 >= E; };
+
+  if (threadIdx.x == 32 * NCW && g.warm > 0 && !g.independent && cl < g.n_chunks) {
+    // The load lane asks L2 for the boxes of its first stages while the preceding kernel drains.
+    Gw8Walk walk(cl * per_chunk + s0, cl * per_chunk + s1, g);
+    Gw8Segment seg;
+    int left = g.warm;
+    while (left > 0 && walk.next(seg)) {
+      const int nst = stages_of(seg);
+      for (int i = 0; i < nst && left > 0; ++i, --left) {
+        tma_prefetch_4d(&x_map, seg.ck * 64, seg.ct * g.wt - g.pad_w, 2 * (seg.m0 + PPS * i) - g.pad_h,
+                        seg.ig * g.nb);
+        if (stage_has_pairs(i))
+          tma_prefetch_4d(&dy_map, seg.ck * 64, seg.ct * g.wt, 2 * (seg.m0 + PPS * i - E), seg.ig * g.nb);
+      }
+    }
+  }
+  if (!g.independent) grid_dependency_wait();
+  grid_dependency_launch_dependents();
 
   if (warp == NCW) {
     // ------------------------------------------------------------ load warp

@@ -353,6 +353,17 @@ int prefill_setting() {
   return v;
 }
 
+// Stages whose boxes a kernel asks L2 for before it waits for its predecessors (Gw8Geom::warm);
+// SPIO_WARM=<n> changes it, 0 switches the requests off.
+int warm_setting() {
+  static const int v = [] {
+    const char* e = getenv("SPIO_WARM");
+    const int n = e ? atoi(e) : 2;
+    return n >= 0 && n <= 16 ? n : 2;
+  }();
+  return v;
+}
+
 // Pairs per CTA from which the dynamic tail is used.
 int dyn_min_pairs() {
   static const int v = [] {
@@ -543,6 +554,7 @@ int make_plan_once(int kind, const spio_gw8_shape* sh, const spio_gw8_tune* tune
   // the start-up window pays on the forward kernel's ordinary layout only: measured, it gains about
   // 0.7 us per launch there, loses as much on paired 7x7 images and does nothing for the weight gradient
   g.prefill = fwd && !pair && prefill_setting() < pl.ns ? prefill_setting() : 0;
+  g.warm = gw8_pdl_enabled() ? warm_setting() : 0;
   g.nblk = cdiv(g.wt, 16);
   g.ntiles = pair ? g.nb / 2 : g.nb * tiles_needed(g.ncb);
   g.pair_images = pair ? 1 : 0;

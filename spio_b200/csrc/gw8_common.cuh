@@ -71,6 +71,10 @@ struct Gw8Geom {
                        // slot competes with its later slots (and all other CTAs') for the memory system
                        // and lands after about 3 us; requested with one companion it lands in about half
                        // that, and the compute warps start that much earlier.
+  int warm;            // stages whose boxes the load lane asks L2 for BEFORE the kernel waits for its
+                       // predecessors (0 = none): the requests overlap the predecessor's tail, warm the
+                       // TLB, and the first loads after the wait hit L2.  Measured without it: the first
+                       // stage lands 3-4 us after the wait has passed, of which about 1 us is the transfer.
   int chunk_inner;     // fprop/dgrad: order of the flattened work.  0: chunk, image group, column
                        // tile, pair (a CTA stays in one 64-channel chunk); 1: image group, column
                        // tile, chunk, pair (a CTA does all chunks of an image one after the other,

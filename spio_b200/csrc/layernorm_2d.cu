@@ -8,7 +8,7 @@
 // HBM-bound: one pass over x (and dy) with 16-byte accesses.  A pixel is handled by a group
 // of T lanes (T = 4, 8, 16 or 32, chosen so that each lane owns at most 4 pieces of 8
 // channels); all statistics are fp32 and reduced by xor shuffles inside the group; weight and
-// bias live in registers for the thread's whole grid-stride loop.  The backward kernel keeps
+// bias live in shared memory.  The backward kernel keeps
 // the per-channel sums of a thread in registers, combines the groups of a warp by shuffles and
 // the warps of a CTA through shared memory, and writes one partial per CTA; a second kernel
 // adds the partials in a fixed order (no atomics, bit-reproducible).
@@ -32,6 +32,7 @@ namespace {
 
 constexpr int kLnThreads = 256;
 constexpr int kMaxPieces = 4;  // 16-byte pieces of a pixel per lane
+constexpr int kMaxChannels = 32 * kMaxPieces * 8;
 
 __device__ __forceinline__ float group_sum(float v, int t) {
   for (int d = t >> 1; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
@@ -48,19 +49,6 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
-// f = p[8 * piece .. 8 * piece + 7], or `fill` when p is NULL or the piece is out of range.
-__device__ __forceinline__ void load8(float (&f)[8], const float* __restrict__ p, int piece, int pieces,
-                                      float fill) {
-  if (p != nullptr && piece < pieces) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p) + 2 * piece);
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 2 * piece + 1);
-    f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = fill;
-  }
-}
-
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   uint4 u;
   __half2* h = reinterpret_cast<__half2*>(&u);
@@ -69,14 +57,45 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return u;
 }
 
-// K = pieces per lane, t = lanes per pixel (power of two), pieces = c / 8.
+// The 16-byte pieces of one pixel row that this lane owns (zeros where the pixel or the piece is out of range).
 template <int K>
-__global__ void __launch_bounds__(kLnThreads, 2)
+__device__ __forceinline__ void fetch_pieces(uint4 (&u)[K], const uint4* __restrict__ p, long long row,
+                                             long long rows, int lane_in_group, int t, int pieces) {
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int piece = lane_in_group + k * t;
+    u[k] = make_uint4(0u, 0u, 0u, 0u);
+    if (row < rows && piece < pieces) u[k] = __ldcs(p + row * pieces + piece);
+  }
+}
+
+// dst[0 .. c) = src, or `fill` when src is NULL (all threads of the CTA; the caller synchronises).
+__device__ __forceinline__ void stage_vector(float* __restrict__ dst, const float* __restrict__ src, int c, float fill) {
+  for (int i = threadIdx.x; i < c; i += kLnThreads) dst[i] = src != nullptr ? __ldg(src + i) : fill;
+}
+
+__device__ __forceinline__ void read8(float (&f)[8], const float* __restrict__ sm, int piece) {
+  const float4 a = reinterpret_cast<const float4*>(sm)[2 * piece];
+  const float4 b = reinterpret_cast<const float4*>(sm)[2 * piece + 1];
+  f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+}
+
+// K = pieces per lane, t = lanes per pixel (power of two), pieces = c / 8.
+//
+// The kernel is a stream: what limits it is the number of bytes each SM keeps in flight.  Weight and bias
+// therefore sit in shared memory, not in 16 * K registers per thread (three CTAs per SM instead of two),
+// and the pieces of a warp's NEXT pixels are requested before the current ones are worked on.
+template <int K>
+__global__ void __launch_bounds__(kLnThreads, 3)
 layernorm_2d_fwd_kernel(uint4* __restrict__ y, float2* __restrict__ stats, const uint4* __restrict__ x,
                         const float* __restrict__ weight, const float* __restrict__ bias, long long rows,
                         int pieces, int t, float inv_c, float eps) {
+  __shared__ __align__(16) float sw[kMaxChannels], sb[kMaxChannels];
   grid_dependency_wait();
   grid_dependency_launch_dependents();
+  stage_vector(sw, weight, pieces * 8, 1.f);
+  stage_vector(sb, bias, pieces * 8, 0.f);
+  __syncthreads();
   const int lane_in_group = threadIdx.x & (t - 1);
   // All lanes of a warp run the same number of iterations (the shuffles below name every
   // lane); a group whose pixel lies past the end works on zeros and stores nothing.
@@ -85,29 +104,20 @@ layernorm_2d_fwd_kernel(uint4* __restrict__ y, float2* __restrict__ stats, const
   const long long warp_step = (long long)gridDim.x * (kLnThreads / 32) * groups_per_warp;
   const int group_in_warp = (threadIdx.x & 31) / t;
 
-  float w[K][8], b[K][8];
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const int piece = lane_in_group + k * t;
-    load8(w[k], weight, piece, pieces, 1.f);
-    load8(b[k], bias, piece, pieces, 0.f);
-  }
-
+  uint4 nxt[K];
+  fetch_pieces<K>(nxt, x, warp_first + group_in_warp, rows, lane_in_group, t, pieces);
   for (long long base = warp_first; base < rows; base += warp_step) {
     const long long row = base + group_in_warp;
     const bool valid = row < rows;
-    const uint4* xr = x + row * pieces;
     float v[K][8];
     float sum = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      const int piece = lane_in_group + k * t;
-      uint4 u = make_uint4(0u, 0u, 0u, 0u);
-      if (valid && piece < pieces) u = __ldcs(xr + piece);
-      unpack8(u, v[k]);
+      unpack8(nxt[k], v[k]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) sum += v[k][i];
     }
+    fetch_pieces<K>(nxt, x, row + warp_step, rows, lane_in_group, t, pieces);
     const float mean = group_sum(sum, t) * inv_c;
     float sq = 0.f;
 #pragma unroll
@@ -127,9 +137,11 @@ layernorm_2d_fwd_kernel(uint4* __restrict__ y, float2* __restrict__ stats, const
     for (int k = 0; k < K; ++k) {
       const int piece = lane_in_group + k * t;
       if (valid && piece < pieces) {
-        float o[8];
+        float o[8], w[8], b[8];
+        read8(w, sw, piece);
+        read8(b, sb, piece);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = (v[k][i] - mean) * rstd * w[k][i] + b[k][i];
+        for (int i = 0; i < 8; ++i) o[i] = (v[k][i] - mean) * rstd * w[i] + b[i];
         yr[piece] = pack8(o);
       }
     }
@@ -137,59 +149,61 @@ layernorm_2d_fwd_kernel(uint4* __restrict__ y, float2* __restrict__ stats, const
 }
 
 // Partials: part[cta][0][c] = sum of dy * xhat, part[cta][1][c] = sum of dy over the CTA's pixels.
+// The weight sits in shared memory, as in the forward kernel; the per-channel sums stay in registers.
 template <int K>
 __global__ void __launch_bounds__(kLnThreads, 2)
 layernorm_2d_bwd_kernel(uint4* __restrict__ dx, float* __restrict__ part, const uint4* __restrict__ dy,
                         const uint4* __restrict__ x, const float2* __restrict__ stats,
                         const float* __restrict__ weight, long long rows, int pieces, int t, float inv_c) {
   extern __shared__ float red[];  // [warps][2][c]
+  __shared__ __align__(16) float sw[kMaxChannels];
   grid_dependency_wait();
   grid_dependency_launch_dependents();
+  const int c = pieces * 8;
+  stage_vector(sw, weight, c, 1.f);
+  __syncthreads();
   const int lane_in_group = threadIdx.x & (t - 1);
   // as in the forward kernel: uniform trip count per warp, out-of-range groups work on zeros
   const int groups_per_warp = 32 / t;
   const long long warp_first = (((long long)blockIdx.x * kLnThreads + threadIdx.x) >> 5) * groups_per_warp;
   const long long warp_step = (long long)gridDim.x * (kLnThreads / 32) * groups_per_warp;
   const int group_in_warp = (threadIdx.x & 31) / t;
-  const int c = pieces * 8;
 
-  float w[K][8], gw[K][8], gb[K][8];
+  float gw[K][8], gb[K][8];
 #pragma unroll
-  for (int k = 0; k < K; ++k) {
-    load8(w[k], weight, lane_in_group + k * t, pieces, 1.f);
+  for (int k = 0; k < K; ++k)
 #pragma unroll
     for (int i = 0; i < 8; ++i) gw[k][i] = gb[k][i] = 0.f;
-  }
 
+  // the operands stay packed (fp16) between the two passes to keep the register count low
+  uint4 nx[K], nd[K];
+  float2 nst = make_float2(0.f, 0.f);
+  {
+    const long long row = warp_first + group_in_warp;
+    fetch_pieces<K>(nx, x, row, rows, lane_in_group, t, pieces);
+    fetch_pieces<K>(nd, dy, row, rows, lane_in_group, t, pieces);
+    if (row < rows) nst = stats[row];
+  }
   for (long long base = warp_first; base < rows; base += warp_step) {
     const long long row = base + group_in_warp;
     const bool valid = row < rows;
-    const float2 st = valid ? stats[row] : make_float2(0.f, 0.f);
-    const uint4* xr = x + row * pieces;
-    const uint4* dr = dy + row * pieces;
-    // the operands stay packed (fp16) between the two passes to keep the register count low
+    const float2 st = nst;
     uint4 ux[K], ud[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) ux[k] = nx[k], ud[k] = nd[k];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int piece = lane_in_group + k * t;
-      ux[k] = make_uint4(0u, 0u, 0u, 0u);
-      ud[k] = make_uint4(0u, 0u, 0u, 0u);
-      if (valid && piece < pieces) {
-        ux[k] = __ldcs(xr + piece);
-        ud[k] = __ldcs(dr + piece);
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const bool on = valid && lane_in_group + k * t < pieces;
-      float xv[8], dv[8];
+      const bool on = valid && piece < pieces;
+      float xv[8], dv[8], w[8];
       unpack8(ux[k], xv);
       unpack8(ud[k], dv);
+      read8(w, sw, on ? piece : 0);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float xh = on ? (xv[i] - st.x) * st.y : 0.f;
-        const float g = dv[i] * w[k][i];
+        const float g = dv[i] * w[i];
         s1 += g;
         s2 += g * xh;
         gw[k][i] += dv[i] * xh;
@@ -203,17 +217,23 @@ layernorm_2d_bwd_kernel(uint4* __restrict__ dx, float* __restrict__ part, const 
     for (int k = 0; k < K; ++k) {
       const int piece = lane_in_group + k * t;
       if (valid && piece < pieces) {
-        float xv[8], dv[8], o[8];
+        float xv[8], dv[8], w[8], o[8];
         unpack8(ux[k], xv);
         unpack8(ud[k], dv);
+        read8(w, sw, piece);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float xh = (xv[i] - st.x) * st.y;
-          o[i] = st.y * (dv[i] * w[k][i] - s1 - xh * s2);
+          o[i] = st.y * (dv[i] * w[i] - s1 - xh * s2);
         }
         or_[piece] = pack8(o);
       }
     }
+    // (requesting the next pixels before working on these ones, as the forward kernel does, made this
+    // kernel spill and cost 15 % at 96 channels: the per-channel sums already fill the registers)
+    fetch_pieces<K>(nx, x, row + warp_step, rows, lane_in_group, t, pieces);
+    fetch_pieces<K>(nd, dy, row + warp_step, rows, lane_in_group, t, pieces);
+    nst = row + warp_step < rows ? stats[row + warp_step] : make_float2(0.f, 0.f);
   }
 
   // groups of a warp own the same channels: add them (lane bits t .. 16), then the warps
@@ -279,7 +299,7 @@ struct LnPlan {
   int pieces, t, k, grid;
 };
 
-int ln_plan(long long rows, int c, LnPlan* p) {
+int ln_plan(long long rows, int c, int ctas_per_sm, LnPlan* p) {
   if (rows <= 0) return jit_fail("rows must be positive");
   if (c <= 0 || c % 8 != 0) return jit_fail("Number of channels must be a multiple of 8.");
   p->pieces = c / 8;
@@ -294,7 +314,7 @@ int ln_plan(long long rows, int c, LnPlan* p) {
     return jit_fail("CUDA error: no device");
   const long long groups_per_cta = kLnThreads / t;
   long long want = (rows + groups_per_cta - 1) / groups_per_cta;
-  const long long cap = (long long)sms * 4;  // a few CTAs per SM: weights are loaded once per thread
+  const long long cap = (long long)sms * ctas_per_sm;  // one wave of resident CTAs, each a grid-stride loop
   p->grid = (int)(want < cap ? want : cap);
   return 0;
 }
@@ -330,7 +350,7 @@ int spio_layernorm_2d_fwd(void* y, float* stats, const void* x, const float* wei
     return jit_fail("tensor pointers must be 16-byte aligned");
   if ((reinterpret_cast<size_t>(stats) & 7u) != 0) return jit_fail("stats must be 8-byte aligned");
   LnPlan p;
-  if (ln_plan(rows, c, &p)) return 1;
+  if (ln_plan(rows, c, 3, &p)) return 1;
   const void* fn[4] = {(const void*)&layernorm_2d_fwd_kernel<1>, (const void*)&layernorm_2d_fwd_kernel<2>,
                        (const void*)&layernorm_2d_fwd_kernel<3>, (const void*)&layernorm_2d_fwd_kernel<4>};
   float inv_c = 1.f / (float)c;
@@ -340,7 +360,7 @@ int spio_layernorm_2d_fwd(void* y, float* stats, const void* x, const float* wei
 
 size_t spio_layernorm_2d_bwd_scratch_bytes(long long rows, int c) {
   LnPlan p;
-  if (ln_plan(rows, c, &p)) return 0;
+  if (ln_plan(rows, c, 2, &p)) return 0;
   return (size_t)p.grid * 2 * c * sizeof(float);
 }
 
@@ -351,7 +371,7 @@ int spio_layernorm_2d_bwd(void* dx, float* dweight, float* dbias, const void* dy
   if (((reinterpret_cast<size_t>(dx) | reinterpret_cast<size_t>(dy) | reinterpret_cast<size_t>(x)) & 15u) != 0)
     return jit_fail("tensor pointers must be 16-byte aligned");
   LnPlan p;
-  if (ln_plan(rows, c, &p)) return 1;
+  if (ln_plan(rows, c, 2, &p)) return 1;
   const size_t need = (size_t)p.grid * 2 * c * sizeof(float);
   if (scratch == nullptr || scratch_bytes < need) return jit_fail("LayerNorm2d scratch buffer is too small");
   const void* fn[4] = {(const void*)&layernorm_2d_bwd_kernel<1>, (const void*)&layernorm_2d_bwd_kernel<2>,
@@ -360,7 +380,7 @@ int spio_layernorm_2d_bwd(void* dx, float* dweight, float* dbias, const void* dy
   float inv_c = 1.f / (float)c;
   void* args[] = {&dx, &part, (void*)&dy, (void*)&x, (void*)&stats, (void*)&weight, &rows, &p.pieces, &p.t, &inv_c};
   const size_t smem = (size_t)(kLnThreads / 32) * 2 * c * sizeof(float);
-  if (smem > 48 * 1024) {
+  if (smem + sizeof(float) * kMaxChannels > 48 * 1024) {
     const cudaError_t ea = cudaFuncSetAttribute(fn[p.k - 1], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ea != cudaSuccess) return jit_fail(std::string("CUDA error: ") + cudaGetErrorString(ea));
   }

@@ -145,6 +145,15 @@ __device__ __forceinline__ void tma_load_4d(u32 dst, const void* tmap, u32 bar, 
       : "memory");
 }
 
+// Asks the L2 cache for the box a later tma_load_4d with the same coordinates will read.  Nothing
+// reaches the SM, so it may be issued before griddepcontrol.wait: L2 is the point of coherence, a line
+// that an earlier kernel still writes after the prefetch is updated in place.
+__device__ __forceinline__ void tma_prefetch_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tmap), "r"(c0),
+               "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
 // L2 eviction-priority policies for loads: 0 = none, 1 = evict first (data that is not read
 // again soon), 2 = evict last (data the next kernel reads again).
 enum { L2_HINT_NONE = 0, L2_HINT_EVICT_FIRST = 1, L2_HINT_EVICT_LAST = 2 };
