@@ -1,4 +1,4 @@
-"""The binding a maintainer of the reference would add to use libspio_b200 (shown in INTEGRATION.md).
+"""The binding a maintainer of the reference would add to use libspio_b200 (the integration guide shows it).
 
 Drop this file into the reference as ``spio/kernels/b200_kernel.py``: :class:`B200Kernel` has the call
 protocol of the reference's ``spio.kernels.Kernel`` (``compile`` / ``load`` / ``__call__`` with the

@@ -147,3 +147,66 @@ def test_dynamic_tail_gives_identical_results():
         os.remove(path)
     for other in results[1:]:
         assert torch.equal(results[0][0], other[0]) and torch.equal(results[0][1], other[1])
+
+
+def test_start_up_settings_give_identical_results():
+    """SPIO_WARM (boxes requested from L2 before the kernel waits for its predecessors) and
+    SPIO_PREFILL (stages requested before the load lane waits for the first one to land) change
+    when data is asked for, never what is computed: fprop, dgrad and wgrad of a chain of dependent
+    launches, in which each launch reads what the one before it wrote, must give the same bits with
+    the requests and the window switched off, at their defaults, and at larger values."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+
+    code = textwrap.dedent("""
+        import sys, torch
+        from oracle import oracle as O
+        from tests import capi
+        sh = O.Shape(24, 136, 30, 30, 3, 3, 1, 1)
+        x, w, b, dy = O.make_inputs(sh, seed=33, bias=True)
+        xd, wd, bd, dyd = (capi.to_dev(t) for t in (x, w, b, dy))
+        ws = (wd.float() * 0.5).half().contiguous(memory_format=torch.channels_last)
+        # Every launch consumes the output of the launch before it, and the launches follow each other
+        # without anything in between (outputs are allocated first): a request that ran ahead of the
+        # producer and were served stale data would show up here.
+        import ctypes
+        from spio_b200 import _clib
+        lib = _clib.load()
+        s = capi.cshape(sh); sp = ctypes.byref(s)
+        st = torch.cuda.current_stream().cuda_stream
+        mk = lambda: torch.full_like(xd, capi.DEAD_VALUE)
+        y1, y2, y3, g1, g2 = mk(), mk(), mk(), mk(), mk()
+        dw = torch.full((sh.c, 8, sh.r, sh.s), capi.DEAD_VALUE, dtype=torch.float32, device=xd.device).contiguous(memory_format=torch.channels_last)
+        nbytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(sp, None)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=xd.device)
+        torch.cuda.synchronize()
+        for src, dst in ((xd, y1), (y1, y2), (y2, y3)):
+            _clib.check(lib.spio_conv2d_gw8_fprop(dst.data_ptr(), src.data_ptr(), ws.data_ptr(), bd.data_ptr(), sp, None, st))
+        for src, dst in ((y3, g1), (g1, g2)):
+            _clib.check(lib.spio_conv2d_gw8_dgrad(dst.data_ptr(), src.data_ptr(), ws.data_ptr(), sp, None, st))
+        _clib.check(lib.spio_conv2d_gw8_wgrad(dw.data_ptr(), y2.data_ptr(), g2.data_ptr(), sp, None, scratch.data_ptr(), nbytes, st))
+        torch.cuda.synchronize()
+        # and the chain equals the same launches issued one by one with a synchronisation after each
+        z1 = capi.fprop(xd, ws, bd, sh); torch.cuda.synchronize()
+        z2 = capi.fprop(z1, ws, bd, sh); torch.cuda.synchronize()
+        z3 = capi.fprop(z2, ws, bd, sh); torch.cuda.synchronize()
+        h1 = capi.dgrad(z3, ws, sh); torch.cuda.synchronize()
+        h2 = capi.dgrad(h1, ws, sh); torch.cuda.synchronize()
+        assert torch.equal(y3, z3) and torch.equal(g2, h2)
+        assert torch.equal(dw, capi.wgrad(z2, h2, sh))
+        assert capi.status() == 0
+        torch.save([t.cpu() for t in (y3, g2, dw)], sys.argv[1])
+    """)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    results = []
+    for warm, prefill in (("0", "0"), ("2", "2"), ("5", "1"), ("1", "3")):
+        path = os.path.join(root, "tests", f"_warm_{warm}_{prefill}.pt")
+        env = dict(os.environ, SPIO_WARM=warm, SPIO_PREFILL=prefill, PYTHONPATH=root)
+        subprocess.run([sys.executable, "-c", code, path], check=True, env=env, cwd=root, timeout=300)
+        results.append(torch.load(path))
+        os.remove(path)
+    for other in results[1:]:
+        assert all(torch.equal(a, b) for a, b in zip(results[0], other))
+    assert all(torch.isfinite(t.float()).all() for t in results[0])

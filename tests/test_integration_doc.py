@@ -1,4 +1,4 @@
-"""INTEGRATION.md shows the reference-side binding; the text it shows is the text of the file the GPU test
+"""The integration guide shows the reference-side binding; the text it shows is the text of the file the GPU test
 executes (spio_b200/examples/reference_binding.py), line for line."""
 
 import re

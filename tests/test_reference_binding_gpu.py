@@ -1,4 +1,4 @@
-"""The reference-side binding of INTEGRATION.md, executed: ``B200Kernel`` (a ctypes wrapper with the
+"""The reference-side binding that the integration guide shows, executed: ``B200Kernel`` (a ctypes wrapper with the
 call protocol of the reference's ``spio.kernels.Kernel``) against the CPU oracle, and the ``spio``
 import name in a model script written for the reference."""
 
