@@ -397,15 +397,21 @@ conv2d_gw8_wgrad_kernel(const __grid_constant__ TensorMap x_map,
 // dw[k][tap][c] = sum over parts of scratch[chunk(k)][part][k % 64][tap][c] (fp32, or rounded once
 // to fp16 when dw_f16 is set: the parameter's own type, which saves autograd's cast), and, when dbias
 // is not NULL, dbias[k] = sum over parts of the bias sums behind it, added in a fixed order.
-// A block of 256 threads owns 8 float4 columns of a part; thread (cx, q) adds the parts q,
-// q+32, ... of column cx, then the 32 partial sums of a column are combined by two shuffle
-// steps and a pass over shared memory.  Launch with 256 threads and
-// grid = ceil(n_chunks * GW8_PART_FLOATS(taps) / 4 / 8).
-template <int THREADS = 256>
+// A block owns 8 float4 columns of a part at a time (n_groups = ceil(n_chunks * GW8_PART_FLOATS(taps)
+// / 4 / 8) such groups, walked with a grid stride); thread (cx, q) adds the parts q, q + 4 * WARPS, ...
+// of column cx, then the partial sums of a column are combined by two shuffle steps and a pass over
+// shared memory.
+//
+// Launch with 256 threads and one block per group: the fastest reduction, for a weight gradient computed on
+// its own (conv2d_gw8_wgrad_reduce_light_kernel is the form the combined backward call uses).
+template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 conv2d_gw8_wgrad_reduce_kernel(void* __restrict__ dw, float* __restrict__ dbias,
-                               const float* __restrict__ scratch, int c, int taps, int n_parts, int dw_f16) {
-  __shared__ float4 red[8][8];
+                               const float* __restrict__ scratch, int c, int taps, int n_parts, int dw_f16,
+                               int n_groups) {
+  constexpr int WARPS = THREADS / 32;
+  constexpr int QN = 4 * WARPS;  // threads that share a column
+  __shared__ float4 red[WARPS][8];
   // Let an independent successor take SMs as they become free, then wait for the partials.
   grid_dependency_launch_dependents();
   grid_dependency_wait();
@@ -416,61 +422,140 @@ conv2d_gw8_wgrad_reduce_kernel(void* __restrict__ dw, float* __restrict__ dbias,
   const int dw_f4 = 64 * taps * 2;                 // float4 of weight gradient per chunk
   const int chunk_f4 = GW8_PART_FLOATS(taps) / 4;  // float4 per part
   const int n_chunks = (c + 63) / 64;
-  const int col = blockIdx.x * 8 + cx;
-  const int ck = col / chunk_f4;
-  const int e = col - ck * chunk_f4;
-  // where the column goes: a float4 of dw, a float4 of dbias, or nowhere (channels >= c)
-  // With dw_f16 the weight gradient is stored as fp16 (four values = 8 bytes per column); the
-  // bias gradient stays fp32.
-  float4* out = nullptr;
-  uint2* out_h = nullptr;
-  if (ck < n_chunks) {
-    if (e < dw_f4) {
-      if (ck * 64 + e / (taps * 2) < c) {
-        out = reinterpret_cast<float4*>(dw) + (size_t)ck * dw_f4 + e;
-        if (dw_f16) out_h = reinterpret_cast<uint2*>(dw) + (size_t)ck * dw_f4 + e;
+  for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
+    const int col = grp * 8 + cx;
+    const int ck = col / chunk_f4;
+    const int e = col - ck * chunk_f4;
+    // where the column goes: a float4 of dw, a float4 of dbias, or nowhere (channels >= c)
+    // With dw_f16 the weight gradient is stored as fp16 (four values = 8 bytes per column); the
+    // bias gradient stays fp32.
+    float4* out = nullptr;
+    uint2* out_h = nullptr;
+    if (ck < n_chunks) {
+      if (e < dw_f4) {
+        if (ck * 64 + e / (taps * 2) < c) {
+          out = reinterpret_cast<float4*>(dw) + (size_t)ck * dw_f4 + e;
+          if (dw_f16) out_h = reinterpret_cast<uint2*>(dw) + (size_t)ck * dw_f4 + e;
+        }
+      } else if (dbias != nullptr && ck * 64 + 4 * (e - dw_f4) < c) {
+        out = reinterpret_cast<float4*>(dbias) + ck * 16 + (e - dw_f4);
       }
-    } else if (dbias != nullptr && ck * 64 + 4 * (e - dw_f4) < c) {
-      out = reinterpret_cast<float4*>(dbias) + ck * 16 + (e - dw_f4);
     }
-  }
-  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (out != nullptr) {
-    const float4* src =
-        reinterpret_cast<const float4*>(scratch) + (size_t)ck * n_parts * chunk_f4 + e;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (out != nullptr) {
+      const float4* src =
+          reinterpret_cast<const float4*>(scratch) + (size_t)ck * n_parts * chunk_f4 + e;
 #pragma unroll 4
-    for (int p = q; p < n_parts; p += 32) {
-      const float4 v = __ldcg(src + (size_t)p * chunk_f4);
-      sum.x += v.x;
-      sum.y += v.y;
-      sum.z += v.z;
-      sum.w += v.w;
+      for (int p = q; p < n_parts; p += QN) {
+        const float4 v = __ldcg(src + (size_t)p * chunk_f4);
+        sum.x += v.x;
+        sum.y += v.y;
+        sum.z += v.z;
+        sum.w += v.w;
+      }
     }
-  }
 #pragma unroll
-  for (int d = 8; d <= 16; d <<= 1) {
-    sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
-    sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
-    sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
-    sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
-  }
-  if (pl == 0) red[wy][cx] = sum;
-  __syncthreads();
-  if (wy == 0 && pl == 0 && out != nullptr) {
+    for (int d = 8; d <= 16; d <<= 1) {
+      sum.x += __shfl_xor_sync(0xffffffffu, sum.x, d);
+      sum.y += __shfl_xor_sync(0xffffffffu, sum.y, d);
+      sum.z += __shfl_xor_sync(0xffffffffu, sum.z, d);
+      sum.w += __shfl_xor_sync(0xffffffffu, sum.w, d);
+    }
+    if (pl == 0) red[wy][cx] = sum;
+    __syncthreads();
+    if (wy == 0 && pl == 0 && out != nullptr) {
 #pragma unroll
-    for (int w = 1; w < 8; ++w) {
-      const float4 v = red[w][cx];
-      sum.x += v.x;
-      sum.y += v.y;
-      sum.z += v.z;
-      sum.w += v.w;
+      for (int w = 1; w < WARPS; ++w) {
+        const float4 v = red[w][cx];
+        sum.x += v.x;
+        sum.y += v.y;
+        sum.z += v.z;
+        sum.w += v.w;
+      }
+      if (out_h != nullptr) {
+        const __half2 lo = __floats2half2_rn(sum.x, sum.y), hi = __floats2half2_rn(sum.z, sum.w);
+        *out_h = make_uint2(*reinterpret_cast<const u32*>(&lo), *reinterpret_cast<const u32*>(&hi));
+      } else {
+        *out = sum;
+      }
     }
-    if (out_h != nullptr) {
-      const __half2 lo = __floats2half2_rn(sum.x, sum.y), hi = __floats2half2_rn(sum.z, sum.w);
-      *out_h = make_uint2(*reinterpret_cast<const u32*>(&lo), *reinterpret_cast<const u32*>(&hi));
-    } else {
-      *out = sum;
+    __syncthreads();  // red is reused by the next group
+  }
+}
+
+// The same reduction in the shape the combined backward call needs.  The blocks of a reduce kernel sit on
+// the SMs, waiting, while the weight-gradient kernel runs, and the input-gradient kernel launched behind
+// them (which does not wait for the reduction) needs 640 x 96 of an SM's 65,536 registers: a waiting block
+// of 256 threads keeps it off that SM until the reduction has finished, one of 128 x 32 registers fits
+// beside it.  So: 128 threads, at most 32 registers, at most one block per SM (grid-stride over the groups
+// of 8 columns).  Thread (cx, q), q < 16, keeps the two sums that threads q and q + 16 of the wide kernel
+// keep, and the 32 sums of a column are added in the wide kernel's order (pairs, pairs of pairs, then the
+// eight groups of four one after the other), so both kernels give the same bits.
+template <int THREADS = 128>  // a template only so that the header can be included in several translation units
+__global__ void __launch_bounds__(THREADS, 2048 / THREADS)
+conv2d_gw8_wgrad_reduce_light_kernel(void* __restrict__ dw, float* __restrict__ dbias,
+                                     const float* __restrict__ scratch, int c, int taps, int n_parts, int dw_f16,
+                                     int n_groups) {
+  static_assert(THREADS == 128, "the column / thread split below assumes 128 threads");
+  __shared__ float4 red[32][8];
+  grid_dependency_launch_dependents();
+  grid_dependency_wait();
+  const int cx = threadIdx.x & 7;
+  const int q = threadIdx.x >> 3;
+  const int dw_f4 = 64 * taps * 2;
+  const int chunk_f4 = GW8_PART_FLOATS(taps) / 4;
+  const int n_chunks = (c + 63) / 64;
+  for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
+    const int col = grp * 8 + cx;
+    const int ck = col / chunk_f4;
+    const int e = col - ck * chunk_f4;
+    float4* out = nullptr;
+    bool half_out = false;
+    if (ck < n_chunks) {
+      if (e < dw_f4) {
+        if (ck * 64 + e / (taps * 2) < c) {
+          out = reinterpret_cast<float4*>(dw) + (size_t)ck * dw_f4 + e;
+          half_out = dw_f16 != 0;
+        }
+      } else if (dbias != nullptr && ck * 64 + 4 * (e - dw_f4) < c) {
+        out = reinterpret_cast<float4*>(dbias) + ck * 16 + (e - dw_f4);
+      }
     }
+    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+    if (out != nullptr) {
+      const float4* src = reinterpret_cast<const float4*>(scratch) + (size_t)ck * n_parts * chunk_f4 + e;
+      for (int p = q; p < n_parts; p += 32) {
+        const float4 v = __ldcg(src + (size_t)p * chunk_f4);
+        lo.x += v.x, lo.y += v.y, lo.z += v.z, lo.w += v.w;
+        if (p + 16 < n_parts) {
+          const float4 u = __ldcg(src + (size_t)(p + 16) * chunk_f4);
+          hi.x += u.x, hi.y += u.y, hi.z += u.z, hi.w += u.w;
+        }
+      }
+    }
+    red[q][cx] = lo;
+    red[q + 16][cx] = hi;
+    __syncthreads();
+    if (q == 0 && out != nullptr) {
+      float4 sum;
+      for (int w = 0; w < 8; ++w) {
+        const float4 a = red[4 * w][cx], b = red[4 * w + 1][cx], cc = red[4 * w + 2][cx], d = red[4 * w + 3][cx];
+        const float4 t = make_float4((a.x + b.x) + (cc.x + d.x), (a.y + b.y) + (cc.y + d.y),
+                                     (a.z + b.z) + (cc.z + d.z), (a.w + b.w) + (cc.w + d.w));
+        if (w == 0)
+          sum = t;
+        else
+          sum.x += t.x, sum.y += t.y, sum.z += t.z, sum.w += t.w;
+      }
+      if (half_out) {
+        const __half2 l2 = __floats2half2_rn(sum.x, sum.y), h2 = __floats2half2_rn(sum.z, sum.w);
+        reinterpret_cast<uint2*>(dw)[(size_t)ck * dw_f4 + e] =
+            make_uint2(*reinterpret_cast<const u32*>(&l2), *reinterpret_cast<const u32*>(&h2));
+      } else {
+        *out = sum;
+      }
+    }
+    __syncthreads();  // red is reused by the next group
   }
 }
 

@@ -364,6 +364,15 @@ int warm_setting() {
   return v;
 }
 
+// SPIO_LIGHT_REDUCE=0: the combined backward call reduces with the wide kernel, as a bare wgrad call does.
+bool light_reduce_enabled() {
+  static const bool v = [] {
+    const char* e = getenv("SPIO_LIGHT_REDUCE");
+    return !(e && e[0] == '0');
+  }();
+  return v;
+}
+
 // Pairs per CTA from which the dynamic tail is used.
 int dyn_min_pairs() {
   static const int v = [] {
@@ -818,14 +827,22 @@ int launch_fwd(int kind, void* out, const void* in, const void* w, const float* 
   return launch_kernel(pl.v->fwd_kernel, pl.grid, pl.threads, pl.smem, stream, args);
 }
 
+// light: the reduction is followed by a kernel that does not wait for it (the input-gradient kernel of the
+// combined backward call); its blocks must then be small enough to sit beside that kernel's CTAs.
 int launch_reduce(void* dw, float* dbias, const float* scratch, int c, int taps, int n_parts,
-                  cudaStream_t stream, int dw_f16 = 0) {
+                  cudaStream_t stream, int dw_f16 = 0, bool light = false, int sms = 0) {
   if (dbias != nullptr && taps % 2 == 0)
     return fail("the fused bias gradient needs an odd number of filter taps (r * s)");
   if ((reinterpret_cast<size_t>(dbias) & 15u) != 0) return fail("dbias must be 16-byte aligned");
   const int total_f4 = cdiv(c, 64) * (GW8_PART_FLOATS(taps) / 4);
-  void* args[] = {&dw, &dbias, &scratch, &c, &taps, &n_parts, &dw_f16};
-  return launch_kernel(reinterpret_cast<const void*>(&conv2d_gw8_wgrad_reduce_kernel<256>), cdiv(total_f4, 8), 256,
+  int n_groups = cdiv(total_f4, 8);
+  void* args[] = {&dw, &dbias, &scratch, &c, &taps, &n_parts, &dw_f16, &n_groups};
+  // The light form walks the groups with at most one block per SM; beyond four passes (more than 256
+  // channels) it is slower than the wide form, and such layers have few parts per column anyway.
+  if (light && sms > 0 && n_groups <= 4 * sms)
+    return launch_kernel(reinterpret_cast<const void*>(&conv2d_gw8_wgrad_reduce_light_kernel<128>),
+                         n_groups < sms ? n_groups : sms, 128, 0, stream, args);
+  return launch_kernel(reinterpret_cast<const void*>(&conv2d_gw8_wgrad_reduce_kernel<256>), n_groups, 256,
                        0, stream, args);
 }
 
@@ -834,7 +851,7 @@ int launch_reduce(void* dw, float* dbias, const float* scratch, int c, int taps,
 int launch_wgrad(void* dw, const void* x, const void* dy, const spio_gw8_shape* sh,
                  const spio_gw8_tune* tune, void* scratch, size_t scratch_bytes,
                  cudaStream_t stream, int hint_x = L2_HINT_NONE, int hint_dy = L2_HINT_NONE,
-                 float* dbias = nullptr, void* jit_fn = nullptr, int dw_f16 = 0) {
+                 float* dbias = nullptr, void* jit_fn = nullptr, int dw_f16 = 0, bool light_reduce = false) {
   if (dw == nullptr || x == nullptr || dy == nullptr) return fail("NULL tensor pointer");
   if (sh == nullptr) return fail("shape is NULL");
   const DeviceInfo* d = nullptr;
@@ -874,7 +891,7 @@ int launch_wgrad(void* dw, const void* x, const void* dy, const spio_gw8_shape* 
     const void* kernel = dbias != nullptr ? pl.v->wgrad_bias_kernel : pl.v->wgrad_kernel;
     if (launch_kernel(kernel, pl.grid, pl.threads, pl.smem, stream, args)) return 1;
   }
-  return launch_reduce(dw, dbias, sc, g.c, sh->r * sh->s, pl.n_parts, stream, dw_f16);
+  return launch_reduce(dw, dbias, sc, g.c, sh->r * sh->s, pl.n_parts, stream, dw_f16, light_reduce, d->sms);
 }
 
 // ---------------------------------------------------------------- host-buffer variants
@@ -1000,7 +1017,8 @@ int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x,
   const bool both = dx != nullptr && dw != nullptr && l2_hints_enabled();
   if (dw != nullptr && launch_wgrad(dw, x, dy, shape, wgrad_tune, scratch, scratch_bytes, st,
                                     both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE,
-                                    both ? L2_HINT_EVICT_LAST : L2_HINT_NONE, dbias, wgrad_fn, o.dw_f16))
+                                    both ? L2_HINT_EVICT_LAST : L2_HINT_NONE, dbias, wgrad_fn, o.dw_f16,
+                                    dx != nullptr && light_reduce_enabled()))
     return 1;
   // Data-parallel: one small kernel stores this rank's dw (and dbias) into every rank's exchange
   // buffer, waits for the others' and overwrites dw with the sum in rank order (2-3 us).  No event,
