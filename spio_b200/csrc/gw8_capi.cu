@@ -632,16 +632,24 @@ int encode_map(CUtensorMap* m, const void* ptr, int c, int w, int h, int n, int 
   // fetching 256 bytes per request is free; with more channels a 256-byte fetch also brings the
   // neighbouring 64-channel chunk of the pixel, which another CTA reads at another time -- measured on
   // 256 x 128 x 56 x 56 fprop under ncu: 309 MB of DRAM reads for 205.5 MB of input, L2 hit rate 5 %.
-  // SPIO_L2_PROMOTION=128 / 256 overrides the choice.
+  // With a channel count that is not a multiple of 64 a pixel (2 c bytes) does not start on a 128-byte line
+  // and its last chunk is shorter than a line, so a 128-byte fetch brings bytes of the neighbouring chunk or
+  // pixel: 64 bytes then.  Measured, 128 -> 64 -> none (32-byte sectors): 256 x 96 x 56 x 56 fprop 79.1 -> 67.8
+  // -> 77.8 us, 256 x 72 x 56 x 56 89.6 -> 86.2 -> 89.7 us, 256 x 160 x 28 x 28 32.3 -> 30.9 -> 32.1 us; the
+  // weight-gradient kernel does not care.
+  // SPIO_L2_PROMOTION=32 / 64 / 128 / 256 overrides the choice.
   static const int forced = [] {
     const char* e = getenv("SPIO_L2_PROMOTION");
     return e ? atoi(e) : 0;
   }();
-  const bool wide = forced ? forced >= 256 : c <= 64;
+  const int bytes = forced ? forced : c <= 64 ? 256 : c % 64 == 0 ? 128 : 64;
+  const CUtensorMapL2promotion promotion = bytes >= 256  ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                           : bytes >= 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                           : bytes >= 64  ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                                          : CU_TENSOR_MAP_L2_PROMOTION_NONE;
   const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(ptr), dims,
                               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B,
-                              wide ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_SWIZZLE_128B, promotion,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char buf[160];
