@@ -5,7 +5,8 @@ torch.profiler with random configuration overlays and trains one XGBoost regress
 from them (scripts/profile_block.py:551-701, scripts/train_performance_model.py:46-142).  Here
 each configuration of a kernel family's configuration space is timed directly with CUDA events,
 in chains of back-to-back launches that rotate over operand sets larger than the L2 cache (the
-way the kernels run in a training step); the fastest goes into the tuning table that
+way the kernels run in a training step; input-gradient and weight-gradient configurations inside
+the combined backward call, whose time is what their rows hold); the fastest goes into the tuning table that
 ``PerformanceModelCache`` consults first, and all rows can be fitted by the small
 gradient-boosted-tree model in ``gbt_model.py`` for shapes that were never measured.
 
@@ -29,7 +30,7 @@ from ..cuda.driver import get_device_attributes
 from .conv2d_gw8_kernel import conv2d_gw8_kernel_factory
 from .conv2d_gw8_params import Conv2dGw8Params
 from .conv2d_gw8_wgrad_kernel import conv2d_gw8_wgrad_kernel_factory
-from .kernel import device_status
+from .kernel import device_status, launch_backward
 from .performance_model_cache import MODEL_DIR, PerformanceModelCache, params_features
 
 KERNELS = {
@@ -62,6 +63,27 @@ def make_operand_sets(kernel_name: str, params: Conv2dGw8Params, device, min_byt
     return out
 
 
+def make_backward_sets(params: Conv2dGw8Params, device, min_bytes: int) -> List[tuple]:
+    """Operand sets of the combined backward call, (dx, dw, x, dy, w, dbias): the input-gradient and
+    the weight-gradient configurations are timed inside that call, next to the other kernel with
+    the planner's defaults, because that is where they run: a configuration that wins a chain of
+    identical launches can lose there (a deeper ring that changes the SM's shared-memory
+    configuration cost the backward call of 256 x 256 x 28 x 28 11 us)."""
+    cl = torch.channels_last
+    w = torch.randn(params.weight_shape, device=device).half().contiguous(memory_format=cl)
+    dw = torch.empty(params.weight_shape, device=device, dtype=torch.float32).contiguous(memory_format=cl)
+    fused_bias = params.has_bias and (params.r * params.s) % 2 == 1
+    dbias = torch.empty(params.k, device=device, dtype=torch.float32) if fused_bias else None
+    per_set = 2 * (2 * params.n * params.c * params.h * params.w + params.n * params.k * params.p * params.q)
+    sets = max(2, -(-min_bytes // per_set))
+    out = []
+    for _ in range(sets):
+        x = torch.randn(params.input_shape, device=device).half().contiguous(memory_format=cl)
+        dy = torch.randn(params.output_shape, device=device).half().contiguous(memory_format=cl)
+        out.append((torch.empty_like(x), dw, x, dy, w, dbias))
+    return out
+
+
 def time_kernel(kernel, operand_sets: List[tuple], reps: int = 3, target_ms: float = 1.0) -> float:
     """Median milliseconds per launch in chains of back-to-back launches over rotating operand
     sets: the way the kernels run in a training step (programmatic dependent launch lets a
@@ -77,6 +99,9 @@ def time_kernel(kernel, operand_sets: List[tuple], reps: int = 3, target_ms: flo
     count = max(4, min(24, int(target_ms / max(start.elapsed_time(stop), 1e-3))))
     times = []
     for _ in range(reps):
+        # a spin kernel holds the stream for about a millisecond while the host queues the chain, so
+        # that the figure is device time even where a call costs the host more than the GPU
+        torch.cuda._sleep(2_000_000)
         start.record()
         for i in range(count):
             kernel(*operand_sets[i % k])
@@ -102,13 +127,27 @@ def tune(kernel_name: str, params: Conv2dGw8Params, device="cuda", max_configs: 
     default = type(configs[0])() if configs else None
     if default is not None and default not in configs:
         configs.insert(0, default)
-    sets = make_operand_sets(kernel_name, params, device, min_bytes=4 * attr.l2_cache_size)
+    backward = not kernel_name.endswith("fprop")
+    sets = (make_backward_sets(params, device, min_bytes=4 * attr.l2_cache_size) if backward
+            else make_operand_sets(kernel_name, params, device, min_bytes=4 * attr.l2_cache_size))
+    partner = None
+    if backward:
+        # the other kernel of the backward call, with the planner's defaults
+        other, other_kwargs = KERNELS["spio_conv2d_gw8_wgrad" if kernel_name.endswith("dgrad") else "spio_conv2d_gw8_dgrad"]
+        partner = other.make_kernel(params, None, attr, **other_kwargs)
+        partner.compile(attr)
+        partner.load(ordinal)
     rows = []
     for cfg in configs:
         kernel = factory.make_kernel(params, cfg, attr, **kwargs)
         kernel.compile(attr)
         kernel.load(ordinal)
-        rows.append((time_kernel(kernel, sets, reps=reps), cfg))
+        if backward:
+            wk, dk = (partner, kernel) if kernel_name.endswith("dgrad") else (kernel, partner)
+            call = lambda dx, dw, x, dy, w, db, wk=wk, dk=dk: launch_backward(wk, dk, dx, dw, x, dy, w, db)  # noqa: E731
+        else:
+            call = kernel
+        rows.append((time_kernel(call, sets, reps=reps), cfg))
     if device_status() != 0:
         raise RuntimeError("a kernel reported a wait time-out while tuning")
     rows.sort(key=lambda r: r[0])
