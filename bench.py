@@ -280,9 +280,13 @@ class LayerPoint:
             with torch.no_grad():
                 keep[i % k] = conv2d_gw8(xs[i % k], w, None, 1, PAD, PAD, 1, groups)
 
+        kept = [None] * k
+
         def step(i):
             y = conv2d_gw8(xs[i % k], w, None, 1, PAD, PAD, 1, groups)
-            torch.autograd.grad(y, (xs[i % k], w), self.b[i % k])
+            # y and the gradients stay alive for k steps: otherwise the allocator hands every step the block
+            # the step before it freed, and outputs rewritten in place partly stay in the L2 cache
+            kept[i % k] = (y, torch.autograd.grad(y, (xs[i % k], w), self.b[i % k]))
 
         for i in range(4):
             step(i)
@@ -348,9 +352,11 @@ class LayerPoint:
             with torch.no_grad():
                 keep[i % k] = F.conv2d(xs[i % k], w, None, 1, PAD, 1, groups)
 
+        kept = [None] * k
+
         def step(i):
             y = F.conv2d(xs[i % k], w, None, 1, PAD, 1, groups)
-            torch.autograd.grad(y, (xs[i % k], w), self.b[i % k])
+            kept[i % k] = (y, torch.autograd.grad(y, (xs[i % k], w), self.b[i % k]))  # as in operator()
 
         try:
             for i in range(3):
