@@ -292,6 +292,36 @@ class LayerPoint:
             step(i)
         fwd_us = chain_us(fwd, count, hold_ms=4.0)
         step_us = chain_us(step, count, hold_ms=12.0)
+        host_step_us = host_us(step, 50)
+        # The same steps, one per operand set, captured into one CUDA graph: what the operator costs the
+        # device when the host is out of the way (recorded launches split their work statically).
+        graph_us = None
+        try:
+            # leaf tensors of the captured steps' own, first used on the capturing stream (autograd
+            # synchronises every backward pass with the stream a leaf was first used on)
+            gxs = [t.detach().requires_grad_(True) for t in self.a]
+            gw = self.w.detach().requires_grad_(True)
+            gkept = [None] * k
+
+            def gstep(i):
+                y = conv2d_gw8(gxs[i % k], gw, None, 1, PAD, PAD, 1, groups)
+                gkept[i % k] = (y, torch.autograd.grad(y, (gxs[i % k], gw), self.b[i % k]))
+
+            side = torch.cuda.Stream(self.dev)
+            side.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(side):
+                gstep(0)
+            torch.cuda.current_stream(self.dev).wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(k):
+                    gstep(i)
+            graph.replay()
+            graph_us = chain_us(lambda i: graph.replay(), max(2, count // k), reps=3) / k
+            del graph
+        except Exception as exc:  # a figure less, not a failed run
+            graph_us = f"not captured: {str(exc)[:120]}"
         params = Conv2dGw8Params(n=self.n, c=self.c, h=self.hw, w=self.hw, padding=PAD, r=R, s=S)
         chosen = {}
         for name, fac, kw in (("fprop", conv2d_gw8_kernel_factory, {}), ("dgrad", conv2d_gw8_kernel_factory, {"igrad": True}),
@@ -299,7 +329,8 @@ class LayerPoint:
             kern = fac.get_kernel(params, self.dev, **kw)
             chosen[name] = {f: v for f, v in kern.config.as_tune().items() if v} if kern.config is not None else {}
         return {"fprop": self._rate(fwd_us), "step": dict(self._rate(step_us / 3.0), us=step_us),
-                "backward_us": step_us - fwd_us, "host_us_per_step": host_us(step, 50), "configs": chosen}
+                "backward_us": step_us - fwd_us, "host_us_per_step": host_step_us,
+                "cuda_graph_step_us": graph_us, "configs": chosen}
 
     def incumbent(self, count: int = 24) -> dict:
         """The REFERENCE's own kernels for this shape (compiled for sm_100a into oracle/_ref by
