@@ -4,7 +4,7 @@ Importing the package touches neither CUDA nor the native library; both are load
 first use (the reference initialises the driver at import, spio/__init__.py:8-14).
 """
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 supported_arch = ["sm_100a"]
 
