@@ -245,6 +245,12 @@ class LayerPoint:
                 fn(i)
             us = chain_us(fn, count)
             res[name] = self._rate(us)
+        # warm variant: every launch works on the same operand set, so whatever part of it fits in the
+        # 126 MB L2 is found there (a layer's input is usually what the kernel before it just wrote);
+        # the rate may exceed the HBM roofline and is labelled, not compared with it
+        res["warm_l2"] = {name: dict(self._rate(chain_us(lambda i, fn=fn: fn(0), count)),
+                                     note="same operand set every launch; not an HBM figure")
+                          for name, fn in (("fprop", fprop), ("dgrad", dgrad), ("wgrad", wgrad))}
         def backward(i):
             chk(lib.spio_conv2d_gw8_backward(self.out[i % k].data_ptr(), self.dw.data_ptr(), None,
                                              self.a[i % k].data_ptr(), self.b[i % k].data_ptr(), self.w.data_ptr(),
