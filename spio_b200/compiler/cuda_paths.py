@@ -19,7 +19,7 @@ CSRC_DIR = Path(__file__).resolve().parent.parent / "csrc"
 
 # The device-only headers a kernel translation unit includes.
 KERNEL_HEADER_NAMES = ("ptx.cuh", "gw8_common.cuh", "conv2d_gw8_fwd.cuh", "conv2d_gw8_wgrad.cuh",
-                       "conv2d_gw8_fwd_tc.cuh", "typed.h", "typed_tma.cuh")
+                       "conv2d_gw8_fwd_tc.cuh", "typed.h", "typed_tma.cuh", "typed_mma.cuh")
 
 
 def _package_dir(name: str) -> Optional[Path]:

@@ -4,7 +4,9 @@ Counterpart of the reference's ``spio.generators`` (generators.py:17-223, tensor
 compound_index.py:14-93, dim.py, fold.py), rebuilt on the compact typed-dimension headers in
 ``spio_b200/csrc/typed.h`` and extended with what sm_100a kernels are made of: tiled TMA tensor
 maps with typed coordinates (:class:`TensorMapSpec`), shared-memory rings guarded by mbarriers
-(:class:`MbarrierRing`) and the tile configuration of the gw8 kernels (:class:`TileConfig`).
+(:class:`MbarrierRing`) and the tile configuration of the gw8 kernels (:class:`TileConfig`); typed
+matrix fragments of the warp-level MMA (:class:`Fragment`), named constants (:class:`ParamsSpec`) and
+macros (:class:`Macro`) as the reference has them.
 
     g = Generators()
     g.C = Dim()
@@ -14,11 +16,13 @@ maps with typed coordinates (:class:`TensorMapSpec`), shared-memory rings guarde
     header = generate(g)            # text of a header; hand it to compile_kernel(header_dict=...)
 """
 
-from .specs import (BUILTIN_DIM_NAMES, CompoundIndex, Dim, Dims, Fold, GenSpec, Generators, MbarrierRing, Strides,
-                    Tensor, TensorMapSpec, TileConfig, dtype, extract_specs, generate, generate_from_source)
+from .specs import (BUILTIN_DIM_NAMES, CompoundIndex, Dim, Dims, Fold, Fragment, FragmentType, GenSpec, Generators,
+                    Macro, MbarrierRing, ParamsSpec, Strides, Tensor, TensorMapSpec, TileConfig, dtype, extract_specs,
+                    generate, generate_from_source)
 from .gw8 import gw8_kernel_specs, gw8_translation_unit
 
-GENERATORS = ["Dim", "Fold", "Tensor", "CompoundIndex", "TensorMapSpec", "MbarrierRing", "TileConfig"]
+GENERATORS = ["Dim", "Fold", "Tensor", "CompoundIndex", "TensorMapSpec", "MbarrierRing", "TileConfig", "Fragment",
+              "ParamsSpec", "Macro"]
 
-__all__ = GENERATORS + ["BUILTIN_DIM_NAMES", "Dims", "Strides", "GenSpec", "Generators", "dtype", "generate",
+__all__ = GENERATORS + ["BUILTIN_DIM_NAMES", "Dims", "Strides", "FragmentType", "GenSpec", "Generators", "dtype", "generate",
                         "extract_specs", "generate_from_source", "gw8_kernel_specs", "gw8_translation_unit"]

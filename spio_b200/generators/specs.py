@@ -353,6 +353,83 @@ class TileConfig(GenSpec):
                 f"{self.tiles}, {self.pps}>;")
 
 
+class FragmentType(Enum):
+    """Warp-level MMA fragments (fp16 x fp16 -> fp32), named as in the reference
+    (spio/generators/fragment_type.py): (C++ template, what its two dimensions are)."""
+
+    M16_N8_F32_C = ("MmaM16N8F32C", ("row", "col"))
+    M16_K16_F16_A = ("MmaM16K16F16A", ("row", "k"))
+    N8_K16_F16_B = ("MmaN8K16F16B", ("col", "k"))
+    M16_K8_F16_A = ("MmaM16K8F16A", ("row", "k"))
+    N8_K8_F16_B = ("MmaN8K8F16B", ("col", "k"))
+
+
+class Fragment(GenSpec):
+    """A matrix fragment whose rows / columns / k are typed dimensions:
+    ``using Acc = MmaM16N8F32C<I, J>;``.  ``first`` and ``second`` are the two dimensions in the
+    order the fragment type names them (C: row, column; A: row, k; B: column, k)."""
+
+    def __init__(self, fragment_type: FragmentType, first: "DimLike", second: "DimLike", name: Optional[str] = None):
+        if not isinstance(fragment_type, FragmentType):
+            raise ValueError("fragment_type must be a FragmentType")
+        self.fragment_type = fragment_type
+        self.first = _dim_from_name(first) if isinstance(first, str) else first
+        self.second = _dim_from_name(second) if isinstance(second, str) else second
+        self.class_name = name
+
+    def used(self) -> List[GenSpec]:
+        return [self.first, self.second]
+
+    def declaration(self) -> str:
+        return (f"using {self._need_name()} = {NAMESPACE}::{self.fragment_type.value[0]}<"
+                f"{self.first._need_name()}, {self.second._need_name()}>;")
+
+
+class ParamsSpec(GenSpec):
+    """Named compile-time constants: ``namespace Block { inline constexpr int p = 16; ... }``
+    (bool, int or float values; the reference's ParamsSpec, spio/generators/params.py)."""
+
+    def __init__(self, params: Dict[str, object], name: Optional[str] = None):
+        for key, val in params.items():
+            if not key.isidentifier():
+                raise ValueError(f"{key!r} is not a C++ identifier")
+            if not isinstance(val, (bool, int, float)):
+                raise ValueError(f"parameter {key} has unsupported type {type(val).__name__}")
+        self.params = dict(params)
+        self.class_name = name
+
+    def declaration(self) -> str:
+        lines = [f"namespace {self._need_name()} {{"]
+        for key, val in self.params.items():
+            if isinstance(val, bool):
+                lines.append(f"inline constexpr bool {key} = {'true' if val else 'false'};")
+            elif isinstance(val, int):
+                lines.append(f"inline constexpr int {key} = {val};")
+            else:
+                lines.append(f"inline constexpr float {key} = {val!r}f;")
+        lines.append("}")
+        return "\n".join(lines)
+
+
+class Macro(GenSpec):
+    """Preprocessor definitions: ``#define NAME value`` (the reference's Macro,
+    spio/generators/macros.py).  Macros have no type name; a container names them only to keep
+    them apart."""
+
+    def __init__(self, macros: Dict[str, object], name: Optional[str] = None):
+        for key in macros:
+            if not key.isidentifier():
+                raise ValueError(f"{key!r} is not a macro name")
+        self.macros = dict(macros)
+        self.class_name = name
+
+    def _need_name(self) -> str:
+        return self.class_name or "macros_" + "_".join(self.macros)
+
+    def declaration(self) -> str:
+        return "\n".join(f"#define {key} {val}" for key, val in self.macros.items())
+
+
 class Generators:
     """Collects specifications; the attribute name becomes the C++ type name (the reference's
     container works the same way, spio/generators/generators_class.py:17-97)."""
@@ -425,6 +502,8 @@ def generate(specs: Iterable[GenSpec], namespace: Optional[str] = None, tma: Opt
     if any(getattr(s, "data_type", None) in (dtype.half, dtype.half2) for s in ordered):
         lines.append("#include <cuda_fp16.h>")
     lines.append('#include "typed_tma.cuh"' if tma else '#include "typed.h"')
+    if any(isinstance(s, Fragment) for s in ordered):
+        lines.append('#include "typed_mma.cuh"')
     if any(isinstance(s, TileConfig) for s in ordered):
         lines.append('#include "gw8_common.cuh"')
     lines.append("")
@@ -447,7 +526,8 @@ def extract_specs(source: str) -> Generators:
     g = Generators()
     scope = {"__builtins__": {}, "dtype": dtype, "Dims": Dims, "Strides": Strides, "Dim": Dim, "Fold": Fold,
              "Tensor": Tensor, "CompoundIndex": CompoundIndex, "TensorMapSpec": TensorMapSpec,
-             "MbarrierRing": MbarrierRing, "TileConfig": TileConfig}
+             "MbarrierRing": MbarrierRing, "TileConfig": TileConfig, "Fragment": Fragment,
+             "FragmentType": FragmentType, "ParamsSpec": ParamsSpec, "Macro": Macro, "dict": dict}
     class Naming(dict):
         """Block-level names: a specification is named the moment it is assigned, so that later
         lines of the same block can use it (``I = Dim()`` then ``Dims(I(16))``)."""

@@ -1,7 +1,8 @@
 // Host-side checks of the typed-dimension header (spio_b200/csrc/typed.h) against types generated
 // from the @spio blocks below; compiled with g++ by tests/test_generators.py.  In the spirit of the
 // reference's tutorial lessons (spio/src_tests/tutorial/01_commutativity.cpp ... 05_compound_index.cpp):
-// type safety, position-free subscripting, folding, compound indices.
+// type safety, position-free subscripting, folding, compound indices, and the lane maps of the typed MMA
+// fragments (spio_b200/csrc/typed_mma.cuh; the reference's spio/include/spio/fragment_index.h).
 /*@spio
 I = Dim()
 J = Dim()
@@ -11,6 +12,11 @@ A = Tensor(dtype.float, Dims(I(16), K(32)))
 B = Tensor(dtype.float, Dims(K(32), J(64)))
 Folded = Tensor(dtype.float, Dims(I(4), K8(4), K(8)), Strides(K8=9))
 Threads = CompoundIndex(Dims(I(4), K8(2), J(16)))
+Acc = Fragment(FragmentType.M16_N8_F32_C, I, J)
+AFrag = Fragment(FragmentType.M16_K16_F16_A, I, K)
+BFrag = Fragment(FragmentType.N8_K16_F16_B, J, K)
+Tile = ParamsSpec(dict(rows=16, cols=8, scale=0.5, transposed=False))
+Names = Macro(dict(LESSON_COUNT=6))
 @spio*/
 #include <cstdio>
 #include <type_traits>
@@ -75,6 +81,38 @@ int main() {
   CHECK(t.get<I>() == I(1));
   CHECK(t.get<K8>() == K8(1));
   CHECK(t.get<J>() == J(5));
+  // fragments: every element of the 16 x 8 accumulator belongs to exactly one (lane, register), and the
+  // coordinates are typed (a row is an I, a column a J)
+  static_assert(std::is_same_v<decltype(Acc::row(0, 0)), I> && std::is_same_v<decltype(Acc::col(0, 0)), J>);
+  int seen_c[16][8] = {};
+  for (int lane = 0; lane < 32; ++lane)
+    for (int i = 0; i < Acc::size; ++i) ++seen_c[Acc::row(lane, i).get()][Acc::col(lane, i).get()];
+  for (int r = 0; r < 16; ++r)
+    for (int c = 0; c < 8; ++c) CHECK(seen_c[r][c] == 1);
+  // the A operand: 16 x 16 halves, register j of a lane holds two consecutive k
+  int seen_a[16][16] = {};
+  for (int lane = 0; lane < 32; ++lane)
+    for (int j = 0; j < AFrag::size; ++j)
+      for (int h = 0; h < 2; ++h) ++seen_a[AFrag::row(lane, j).get()][AFrag::k(lane, j).get() + h];
+  for (int r = 0; r < 16; ++r)
+    for (int k = 0; k < 16; ++k) CHECK(seen_a[r][k] == 1);
+  // the row addresses the lanes hand to ldmatrix.x4 cover the four 8 x 8 matrices in register order
+  for (int lane = 0; lane < 32; ++lane) {
+    const int m = lane / 8;  // matrix = destination register
+    CHECK(AFrag::load_row(lane).get() == lane % 8 + 8 * (m % 2));
+    CHECK(AFrag::load_k(lane).get() == 8 * (m / 2));
+    CHECK(AFrag::row(4 * (lane % 8), m).get() == AFrag::load_row(lane).get());
+    CHECK(AFrag::k(0, m).get() == AFrag::load_k(lane).get());
+  }
+  int seen_b[8][16] = {};
+  for (int lane = 0; lane < 32; ++lane)
+    for (int j = 0; j < BFrag::size; ++j)
+      for (int h = 0; h < 2; ++h) ++seen_b[BFrag::col(lane, j).get()][BFrag::k(lane, j).get() + h];
+  for (int c = 0; c < 8; ++c)
+    for (int k = 0; k < 16; ++k) CHECK(seen_b[c][k] == 1);
+  // named constants and macros
+  static_assert(Tile::rows == 16 && Tile::cols == 8 && !Tile::transposed && Tile::scale == 0.5f);
+  static_assert(LESSON_COUNT == 6);
   std::puts("typed lessons ok");
   return 0;
 }

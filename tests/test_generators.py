@@ -191,6 +191,40 @@ def test_typed_kernel_compiles_for_sm_100a_and_misuse_does_not():
         compile_kernel(src.replace("*src[c8][w][h]", "*src[c8][w][n]"), arch=(10, 0), header_dict=header)
 
 
+def test_fragments_params_and_macros():
+    from spio_b200.generators import Fragment, FragmentType, Macro, ParamsSpec
+
+    g = Generators()
+    g.I, g.J, g.K = Dim(), Dim(), Dim()
+    g.Acc = Fragment(FragmentType.M16_N8_F32_C, g.I, g.J)
+    g.AFrag = Fragment(FragmentType.M16_K16_F16_A, g.I, "k")
+    g.Block = ParamsSpec(dict(p=16, unroll=True, eps=1e-6))
+    g.Names = Macro(dict(KERNEL_NAME="my_kernel"))
+    text = generate(g)
+    assert '#include "typed_mma.cuh"' in text
+    lines = body(text)
+    assert f"using Acc = {T}::MmaM16N8F32C<I, J>;" in lines
+    assert f"using AFrag = {T}::MmaM16K16F16A<I, K>;" in lines
+    assert "namespace Block {" in lines and "inline constexpr int p = 16;" in lines
+    assert "inline constexpr bool unroll = true;" in lines and "inline constexpr float eps = 1e-06f;" in lines
+    assert "#define KERNEL_NAME my_kernel" in text.splitlines()
+    with pytest.raises(ValueError):
+        ParamsSpec(dict(name="text"))
+    with pytest.raises(ValueError):
+        Fragment("M16_N8_F32_C", g.I, g.J)
+
+
+def test_typed_mma_kernel_compiles_and_mismatched_fragments_do_not():
+    src = (ROOT / "spio_b200" / "examples" / "typed_mma_tile.cu").read_text()
+    header = {"types.h": generate_from_source(src)}
+    cubin = compile_kernel(src, source_name="typed_mma_tile.cu", arch=(10, 0), header_dict=header)
+    assert len(cubin) > 1000
+    # a B operand whose columns are rows of C: the multiply-accumulate has no such overload
+    wrong = src.replace("BFrag = Fragment(FragmentType.N8_K16_F16_B, J, K)", "BFrag = Fragment(FragmentType.N8_K16_F16_B, I, K)")
+    with pytest.raises(ValueError):
+        compile_kernel(wrong, arch=(10, 0), header_dict={"types.h": generate_from_source(wrong)})
+
+
 def test_gw8_translation_unit_is_generated():
     unit = gw8_translation_unit("spio_conv2d_gw8_fprop__x", False, 3, 3, 2, 2, 2)
     assert unit.splitlines()[:3] == ['#include "conv2d_gw8_fwd.cuh"', "using namespace spio_b200;",

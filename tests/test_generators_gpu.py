@@ -60,3 +60,26 @@ def test_tensor_map_encode_rejects_bad_arguments():
     bad_box = (ctypes.c_uint * 2)(4, 8)
     assert lib.spio_tensor_map_encode(tmap, x.data_ptr(), 2, 2, sizes, strides, bad_box, 0) != 0
     assert "16 bytes" in _clib.last_error()
+
+
+def test_typed_mma_tile_kernel():
+    """spio_b200/examples/typed_mma_tile.cu: typed fragments loaded with ldmatrix from typed
+    shared-memory tensors, multiplied with the warp-level MMA and stored through their typed lane
+    coordinates, against an fp32 matrix product of the same fp16 operands."""
+    source = SOURCE.parent / "typed_mma_tile.cu"
+    src = source.read_text()
+    specs = extract_specs(src)
+    cubin = compile_kernel(src, source_name="typed_mma_tile.cu", header_dict={"types.h": generate(specs)},
+                           arch=get_device_attributes(0).compute_capability)
+    module, fn = load_kernel("typed_mma_tile", cubin, 0)
+    m, n, k = (specs.Shape.params[key] for key in ("m", "n", "k"))
+    gen = torch.Generator(device="cuda:0").manual_seed(3)
+    a = torch.randn(m, k, device="cuda:0", generator=gen).half()
+    b = torch.randn(n, k, device="cuda:0", generator=gen).half()          # k contiguous: B is stored column by column
+    c = torch.full((m, n), capi.DEAD_VALUE, dtype=torch.float32, device="cuda:0")
+    fn.launch(specs.Tiles.size, 32, [a, b, c])
+    torch.cuda.synchronize()
+    ref = a.double() @ b.double().t()
+    # fp32 accumulation over k = 96 products of fp16 values
+    assert float((c.double() - ref).abs().max()) <= 1e-4 * float(ref.abs().max())
+    module.unload()
