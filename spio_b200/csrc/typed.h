@@ -213,6 +213,28 @@ struct Tensor {
   SPIO_HD constexpr T& operator*() const { return *p; }
 };
 
+// ---------------------------------------------------------------- carving tensors out of a buffer
+
+// Hands out typed tensors one after the other from a byte buffer, typically the dynamic shared memory of
+// a kernel: `StackAllocator a(smem); auto x = a.allocate<XTile>(); auto w = a.allocate<WTile, 128>();`.
+// Each tensor starts on an ALIGN-byte boundary (16 by default, what vector loads, ldmatrix rows and bulk
+// copies need; 128 or 1024 for swizzled TMA boxes).  The reference's spio/include/spio/allocator.h does
+// the same with a deallocate that this one leaves out: kernels here carve once.
+struct StackAllocator {
+  unsigned char* next;
+  SPIO_HD explicit StackAllocator(void* base) : next(static_cast<unsigned char*>(base)) {}
+  template <class TensorT, int ALIGN = 16>
+  SPIO_HD TensorT allocate() {
+    static_assert(ALIGN > 0 && (ALIGN & (ALIGN - 1)) == 0, "alignment must be a power of two");
+    using T = typename TensorT::data_type;
+    const unsigned long long at = (reinterpret_cast<unsigned long long>(next) + ALIGN - 1) & ~(unsigned long long)(ALIGN - 1);
+    next = reinterpret_cast<unsigned char*>(at) + sizeof(T) * TensorT::storage_size();
+    return TensorT(reinterpret_cast<T*>(at));
+  }
+  // bytes handed out so far, counted from `base`
+  SPIO_HD long long used(const void* base) const { return next - static_cast<const unsigned char*>(base); }
+};
+
 // ---------------------------------------------------------------- compound index
 
 // Splits a linear offset into typed indices, the first extent varying slowest.  The stride of an

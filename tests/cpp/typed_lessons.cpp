@@ -110,6 +110,17 @@ int main() {
       for (int h = 0; h < 2; ++h) ++seen_b[BFrag::col(lane, j).get()][BFrag::k(lane, j).get() + h];
   for (int c = 0; c < 8; ++c)
     for (int k = 0; k < 16; ++k) CHECK(seen_b[c][k] == 1);
+  // carving typed tensors out of one buffer, each on its alignment
+  alignas(128) unsigned char buffer[4096];
+  spio_b200::typed::StackAllocator alloc(buffer);
+  const A first = alloc.allocate<A>();
+  const Folded second = alloc.allocate<Folded, 128>();
+  CHECK(reinterpret_cast<unsigned char*>(first.get()) == buffer);
+  CHECK(reinterpret_cast<unsigned char*>(second.get()) == buffer + 16 * 32 * 4);  // already a multiple of 128
+  const Folded third = alloc.allocate<Folded, 128>();
+  CHECK((reinterpret_cast<unsigned long long>(third.get()) & 127u) == 0);
+  CHECK(third.get() >= second.get() + Folded::storage_size());
+  CHECK(alloc.used(buffer) <= (long long)sizeof buffer);
   // named constants and macros
   static_assert(Tile::rows == 16 && Tile::cols == 8 && !Tile::transposed && Tile::scale == 0.5f);
   static_assert(LESSON_COUNT == 6);
