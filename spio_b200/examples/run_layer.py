@@ -21,8 +21,9 @@ from spio_b200 import _clib
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kind", choices=["fprop", "dgrad", "wgrad", "layernorm"],
-                    help="layernorm = forward + backward of spio::layernorm_2d on an n x c x hw x hw tensor")
+    ap.add_argument("kind", choices=["fprop", "dgrad", "wgrad", "backward", "layernorm"],
+                    help="backward = the combined call (wgrad, reduce, dgrad); "
+                         "layernorm = forward + backward of spio::layernorm_2d on an n x c x hw x hw tensor")
     ap.add_argument("n", type=int)
     ap.add_argument("c", type=int)
     ap.add_argument("hw", type=int)
@@ -59,6 +60,7 @@ def main() -> None:
     ys = [torch.randn(n, c, hw, hw, device=dev, generator=gen).half().contiguous(memory_format=cl) for _ in range(sets)]
     w = torch.randn(c, 8, r, r, device=dev, generator=gen).half().contiguous(memory_format=cl)
     dw = torch.empty(c, 8, r, r, device=dev, dtype=torch.float32).contiguous(memory_format=cl)
+    dxs = [torch.empty_like(xs[0]) for _ in range(sets)] if args.kind == "backward" else []
     nbytes = lib.spio_conv2d_gw8_wgrad_scratch_bytes(shp, tp if args.kind == "wgrad" else None)
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
@@ -68,6 +70,9 @@ def main() -> None:
             rc = lib.spio_conv2d_gw8_fprop(y.data_ptr(), x.data_ptr(), w.data_ptr(), None, shp, tp, stream)
         elif args.kind == "dgrad":
             rc = lib.spio_conv2d_gw8_dgrad(y.data_ptr(), x.data_ptr(), w.data_ptr(), shp, tp, stream)
+        elif args.kind == "backward":
+            rc = lib.spio_conv2d_gw8_backward(dxs[i % sets].data_ptr(), dw.data_ptr(), None, x.data_ptr(), y.data_ptr(),
+                                              w.data_ptr(), shp, None, None, scratch.data_ptr(), nbytes, stream, None)
         else:
             rc = lib.spio_conv2d_gw8_wgrad(dw.data_ptr(), x.data_ptr(), y.data_ptr(), shp, tp, scratch.data_ptr(),
                                            nbytes, stream)
