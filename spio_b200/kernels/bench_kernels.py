@@ -25,14 +25,17 @@ from .conv2d_stats import Conv2dStats
 from .kernel import device_status
 
 
-def measure(params: Conv2dGw8Params, device: torch.device) -> dict:
-    """{kernel: (microseconds, GB/s, configuration)} with the configuration the factory selects."""
+def measure(params: Conv2dGw8Params, device: torch.device, warm: bool = False) -> dict:
+    """{kernel: (microseconds, GB/s, configuration)} with the configuration the factory selects.
+    ``warm``: two operand sets instead of four L2 sizes' worth, so that small layers stay in the L2
+    cache from launch to launch (the situation inside a network, and the reason the reference's
+    RTX 4090 figure exceeds the DRAM bandwidth at small batch)."""
     attr = get_device_attributes(device.index or 0)
     nbytes = Conv2dStats(params, output_names="output").bytes
     out = {}
     for name, (factory, kwargs) in sorted(KERNELS.items()):
         kernel = factory.get_kernel(params, device, **kwargs)
-        sets = make_operand_sets(name, params, device, min_bytes=4 * attr.l2_cache_size)
+        sets = make_operand_sets(name, params, device, min_bytes=1 if warm else 4 * attr.l2_cache_size)
         ms = time_kernel(kernel, sets, reps=5)
         out[name.replace("spio_conv2d_gw8_", "")] = (ms * 1e3, nbytes / ms / 1e6, kernel.config)
         del sets
@@ -46,6 +49,7 @@ def main(argv: Optional[list] = None) -> None:
     ap.add_argument("--hw", type=int, default=56)
     ap.add_argument("--filter", type=int, default=3)
     ap.add_argument("--batches", default="32,64,96,128,160,192,224,256")
+    ap.add_argument("--warm", action="store_true", help="two operand sets only: small layers stay in the L2 cache")
     ap.add_argument("--csv", default=None, help="also write the rows to this file")
     args = ap.parse_args(argv)
     device = torch.device("cuda", torch.cuda.current_device())
@@ -54,7 +58,7 @@ def main(argv: Optional[list] = None) -> None:
     for n in (int(t) for t in args.batches.split(",")):
         params = Conv2dGw8Params(n=n, c=args.channels, h=args.hw, w=args.hw, r=args.filter, s=args.filter,
                                  padding=args.filter // 2)
-        res = measure(params, device)
+        res = measure(params, device, warm=args.warm)
         print(f"{n:>6} | " + " | ".join(f"{res[k][0]:8.1f} us {res[k][1]:7.0f} GB/s" for k in ("dgrad", "fprop", "wgrad")),
               flush=True)
         for k, (us, gbs, cfg) in res.items():
