@@ -517,7 +517,7 @@ def run_ours(args) -> None:
     px, px_all, collective = None, None, "none (1 GPU)"
     if world > 1:
         collective = "nccl all-reduce on a side stream, overlapped with dgrad"
-        if args.collective == "peer" or (args.collective == "auto" and world <= 4):
+        if args.collective in ("peer", "auto"):
             try:
                 px = px_all = PeerExchange(C * 8 * R * S + C, device=dev)
                 collective = "peer-store exchange inside the launch chain (spio_dp_push / spio_dp_sum)"
@@ -988,8 +988,8 @@ def main() -> None:
     ap.add_argument("--no-sustained", action="store_true", help="skip the 200-step run")
     ap.add_argument("--no-incumbent", action="store_true", help="skip the reference's own kernels")
     ap.add_argument("--collective", choices=["auto", "peer", "nccl"], default="auto",
-                    help="how dw is summed over the ranks (N > 1); auto = the peer-store exchange up to 4 GPUs, "
-                         "NCCL above (measured: equal at 2 and 4 GPUs, NCCL 10 us per step faster at 8)")
+                    help="how dw is summed over the ranks (N > 1); auto = the peer-store exchange inside the launch "
+                         "chain, NCCL if it cannot be set up")
     ap.add_argument("--force-exchange", action="store_true",
                     help="1 GPU: run the peer-store exchange with the rank itself")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,

@@ -1022,6 +1022,21 @@ int spio_conv2d_gw8_backward_ex(void* dx, void* dw, float* dbias, const void* x,
   // Both kernels read dy.  The weight-gradient kernel asks the L2 to keep dy and to let x go
   // first, so that the input-gradient kernel finds as much of dy in the cache as fits; that
   // kernel in turn marks dy as done with.
+  // With the exchange in the chain the input-gradient kernel leaves one SM to each of its CTAs: a waiting
+  // exchange CTA keeps the input-gradient CTA of its SM from starting (measured on 8 GPUs: 135 us per step
+  // with 148 input-gradient CTAs, 115 us with 139).
+  spio_gw8_tune dgrad_dp_tune;
+  if (o.dp != nullptr && dx != nullptr && (dgrad_tune == nullptr || dgrad_tune->grid == 0)) {
+    const DeviceInfo* d = nullptr;
+    if (device_info(&d)) return 1;
+    const int ctas = dp_exchange_ctas(dw_floats + db_floats);
+    if (ctas > 0 && ctas < d->sms / 2) {
+      memset(&dgrad_dp_tune, 0, sizeof dgrad_dp_tune);
+      if (dgrad_tune != nullptr) dgrad_dp_tune = *dgrad_tune;
+      dgrad_dp_tune.grid = d->sms - ctas;
+      dgrad_tune = &dgrad_dp_tune;
+    }
+  }
   const bool both = dx != nullptr && dw != nullptr && l2_hints_enabled();
   if (dw != nullptr && launch_wgrad(dw, x, dy, shape, wgrad_tune, scratch, scratch_bytes, st,
                                     both ? L2_HINT_EVICT_FIRST : L2_HINT_NONE,

@@ -48,6 +48,7 @@ bool gw8_pdl_enabled();                // programmatic dependent launch (SPIO_PD
 int gw8_status_pointer(int** status);  // device address of the current device's status word
 
 // The data-parallel exchange of the weight gradient (dp_exchange.cu).
+int dp_exchange_ctas(size_t n_floats);  // CTAs of one exchange of n floats
 int dp_push(const spio_dp_exchange* dp, const float* a, size_t n_a, const float* b, size_t n_b,
             cudaStream_t stream);
 int dp_sum(const spio_dp_exchange* dp, float* a, size_t n_a, float* b, size_t n_b, cudaStream_t stream);
