@@ -122,7 +122,9 @@ int spio_conv2d_gw8_backward(void* dx, float* dw, float* dbias, const void* x, c
  *     dbias) into every rank's exchange buffer and overwrites them with the sum over the ranks,
  *     added in rank order (bit-identical on all ranks), while the input-gradient kernel runs
  *     beside it.  dw must be fp32.  `dw_ready`, if given, is then recorded after the
- *     input-gradient kernel, whose completion implies that of the sum. */
+ *     input-gradient kernel, whose completion implies that of the sum.  The input-gradient kernel
+ *     is launched on as many SMs fewer as the exchange has CTAs (one per 512 floats), unless
+ *     dgrad_tune names a grid: its CTAs cannot start on an SM where an exchange CTA is waiting. */
 struct spio_dp_exchange;
 typedef struct spio_gw8_backward_opts {
   int dw_f16;
