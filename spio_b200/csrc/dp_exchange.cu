@@ -117,6 +117,8 @@ dp_exchange_kernel(PeerTable peers, float* __restrict__ a, int n_a, float* __res
           return;
         }
       }
+      // a waiting warp shares its SM with a convolution CTA: it steps aside between polls
+      __nanosleep(100);
       lo = load_words(src);
       hi = load_words(src + 1);
     }
