@@ -176,6 +176,16 @@ struct axis_size<D, E, Es...> {
   static constexpr int value = here ? E::size : axis_size<D, Es...>::value;
 };
 
+// Positions, in base units, that the axes of I's dimension cover: the size of the coarsest axis times its unit.
+template <class I, class... Es>
+struct dim_span {
+  static constexpr int value = [] {
+    int unit = 0, size = 0;
+    (((indexes<I, typename Es::dim> && Es::dim::stride > unit) ? (unit = Es::dim::stride, size = Es::size) : 0), ...);
+    return unit * size;
+  }();
+};
+
 }  // namespace detail
 
 // ---------------------------------------------------------------- tensor and cursor
@@ -208,6 +218,22 @@ struct Tensor {
     using math = detail::axis_math<I, Es...>;
     static_assert(math::found, "the tensor has no axis of this index's dimension");
     return math::offset(i.get());
+  }
+  // Whether an index lies inside the tensor along its dimension (counted in the index's own unit: a
+  // folded index is compared with the number of whole folds).  For masks at ragged edges, as the
+  // reference's Tensor::inbounds (spio/include/spio/tensor.h:580-609): `if (X::in_range(h) && X::in_range(w))`.
+  template <class I>
+  SPIO_HD static constexpr bool in_range(I i) {
+    using math = detail::axis_math<I, Es...>;
+    static_assert(math::found, "the tensor has no axis of this index's dimension");
+    return i.get() >= 0 && i.get() * I::stride < detail::dim_span<I, Es...>::value;
+  }
+  template <class I, class... Is>
+  SPIO_HD static constexpr bool inbounds(I i, Is... rest) {
+    if constexpr (sizeof...(Is) == 0)
+      return in_range(i);
+    else
+      return in_range(i) && inbounds(rest...);
   }
   SPIO_HD constexpr T* get() const { return p; }
   SPIO_HD constexpr T& operator*() const { return *p; }

@@ -110,6 +110,11 @@ int main() {
       for (int h = 0; h < 2; ++h) ++seen_b[BFrag::col(lane, j).get()][BFrag::k(lane, j).get() + h];
   for (int c = 0; c < 8; ++c)
     for (int k = 0; k < 16; ++k) CHECK(seen_b[c][k] == 1);
+  // masks at ragged edges: is an index inside the tensor along its dimension?
+  static_assert(A::in_range(I(15)) && !A::in_range(I(16)) && !A::in_range(I(-1)));
+  static_assert(A::inbounds(I(3), K(31)) && !A::inbounds(I(3), K(32)));
+  static_assert(Folded::in_range(K(31)) && !Folded::in_range(K(32)));    // 4 folds of 8
+  static_assert(Folded::in_range(K8(3)) && !Folded::in_range(K8(4)));
   // carving typed tensors out of one buffer, each on its alignment
   alignas(128) unsigned char buffer[4096];
   spio_b200::typed::StackAllocator alloc(buffer);
