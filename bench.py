@@ -662,7 +662,7 @@ def run_ours(args) -> None:
         dp_parity = "ok"
         barrier()
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, period_s=0.0005)
     if rank == 0:
         sampler.start()
     t0 = torch.cuda.Event(enable_timing=True)
